@@ -1,1 +1,1 @@
-from . import llama  # noqa: F401  (registers the architecture)
+from . import llama, tisalorn  # noqa: F401  (register the architectures)

@@ -30,13 +30,16 @@ from .allocators import CacheError, FreeList
 @dataclass(frozen=True)
 class CacheNeed:
     """What one cache entry needs. kind "kv": keys and values of `kv_heads` x `head_dim` per position, all of them
-    (window None) or the last `window`. kind "state": a float32 tensor of `state_shape` per sequence."""
+    (window None) or the last `window`. kind "state": a float32 tensor of `state_shape` per sequence. kind
+    "several": a mixer that keeps more than one thing (keys and values beside a state, two states) lists them in
+    `parts`; the model gives every part a cache entry of its own and hands the mixer their views in that order."""
 
     kind: str
     kv_heads: int = 0
     head_dim: int = 0
     window: int | None = None
     state_shape: tuple[int, ...] = ()
+    parts: tuple["CacheNeed", ...] = ()
 
 
 class KvView:

@@ -50,9 +50,18 @@ def supported_architectures() -> list[str]:
     return sorted(_ARCHITECTURES)
 
 
+def model_type_of(config: Mapping[str, Any]) -> str | None:
+    """The name a config.json chooses its architecture by: `model_type` (Hugging Face configs), else `architecture`
+    (a single name)."""
+    name = config.get("model_type")
+    if name is None and isinstance(config.get("architecture"), str):
+        name = config["architecture"]
+    return name
+
+
 def config_from_dict(config: Mapping[str, Any], generation: Mapping[str, Any] | None = None) -> Any:
-    """The typed configuration of a config.json dict, chosen by its `model_type`."""
-    return architecture(config.get("model_type")).config_class.from_hf(dict(config), generation)
+    """The typed configuration of a config.json dict, chosen by its `model_type` (or `architecture`)."""
+    return architecture(model_type_of(config)).config_class.from_hf(dict(config), generation)
 
 
 def read_config_dicts(folder: str) -> tuple[dict, dict | None]:

@@ -6,7 +6,7 @@
 // ---- embedding: x[r, :] = float(table[token_r, :]) ----------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ tokens,
-                             int hidden, int vocab, int* __restrict__ status) {
+                             int hidden, int vocab, float scale, int* __restrict__ status) {
   int row = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
@@ -17,21 +17,27 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
     return;
   }
   const T* src = table + (size_t)token * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)row * hidden + i] = to_float(src[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)row * hidden + i] = to_float(src[i]) * scale;
 }
 
-DLLM_EXPORT int dllm_embed(float* out, const void* table, const int* tokens, int rows, int hidden, int vocab,
-                           int dtype, int* status, cudaStream_t stream) {
+// x[r, :] = float(table[token_r, :]) * scale (the product in float32; scale 1 is the plain gather).
+DLLM_EXPORT int dllm_embed_scaled(float* out, const void* table, const int* tokens, int rows, int hidden, int vocab,
+                                  int dtype, float scale, int* status, cudaStream_t stream) {
   if (rows <= 0) return DLLM_OK;
   if (hidden <= 0 || vocab <= 0) return DLLM_BAD_ARGUMENT;
   int threads = hidden >= 256 ? 256 : 64;
   if (dtype == DLLM_F32)
     return dllm_launch_pdl(embed_kernel<float>, dim3(rows), dim3(threads), 0, stream, out, (const float*)table,
-                           tokens, hidden, vocab, status);
+                           tokens, hidden, vocab, scale, status);
   if (dtype == DLLM_BF16)
     return dllm_launch_pdl(embed_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, out,
-                           (const __nv_bfloat16*)table, tokens, hidden, vocab, status);
+                           (const __nv_bfloat16*)table, tokens, hidden, vocab, scale, status);
   return DLLM_BAD_ARGUMENT;
+}
+
+DLLM_EXPORT int dllm_embed(float* out, const void* table, const int* tokens, int rows, int hidden, int vocab,
+                           int dtype, int* status, cudaStream_t stream) {
+  return dllm_embed_scaled(out, table, tokens, rows, hidden, vocab, dtype, 1.0f, status, stream);
 }
 
 // ---- RMSNorm: out[r] = x[rows ? rows[r] : r] * (1 / sqrt(mean(x^2) + eps)) * w ---------------------------------------
@@ -342,4 +348,150 @@ DLLM_EXPORT int dllm_mask_tokens(float* logits, int rows, int vocab, const int* 
   if (vocab <= 0 || logits == nullptr || ids == nullptr || produced == nullptr) return DLLM_BAD_ARGUMENT;
   return dllm_launch_pdl(mask_tokens_kernel, dim3(1), dim3(256), 0, stream, logits, rows, vocab, ids, n_ids, produced,
                          steps, min_tokens);
+}
+
+// ---- layer norm without a bias: out[r] = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w -------------------------
+// One block per row: the mean first, then the mean of the squared deviations (two passes, as the definition reads;
+// not E[x^2] - mean^2), both in float32 with a fixed-order block reduction, so a row's bits do not depend on the
+// other rows of the launch. `rows` gathers as in the RMS norm.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  __syncthreads();  // (scratch may still be read from the sum before)
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = lane < warps ? scratch[lane] : 0.f;
+  return warp_sum(total);
+}
+
+template <typename T>
+__global__ void layernorm_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ weight,
+                                 const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) sum += src[i];
+  float mean = block_sum(sum, scratch) / (float)hidden;
+  float squares = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float d = src[i] - mean;
+    squares = fmaf(d, d, squares);
+  }
+  float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)hidden + eps);
+  T* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<T>((src[i] - mean) * inv * weight[i]);
+}
+
+DLLM_EXPORT int dllm_layernorm(void* out, const float* x, const float* weight, const int* rows, int n_rows, int hidden,
+                               float eps, int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return DLLM_OK;
+  if (hidden <= 0) return DLLM_BAD_ARGUMENT;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (out_dtype == DLLM_F32)
+    return dllm_launch_pdl(layernorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (float*)out, x, weight,
+                           rows, hidden, eps);
+  if (out_dtype == DLLM_BF16)
+    return dllm_launch_pdl(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
+                           (__nv_bfloat16*)out, x, weight, rows, hidden, eps);
+  return DLLM_BAD_ARGUMENT;
+}
+
+// ---- gated unit with clamped inputs ------------------------------------------------------------------------------
+// in[r] = [gate (width values) | up (width values)] as the product left them; g = min(gate, limit), u = clamp(up,
+// -limit, limit); out[r, i] = g * sigmoid(alpha * g) * (u + shift), computed in float32, rounded once.
+template <typename T>
+__global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ in, long long total, int width,
+                                   float limit, float alpha, float shift) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i / width;
+    int c = (int)(i - r * width);
+    float g = fminf(to_float(in[r * 2 * width + c]), limit);
+    float u = fminf(fmaxf(to_float(in[r * 2 * width + width + c]), -limit), limit);
+    float s = 1.0f / (1.0f + expf(-alpha * g));
+    out[i] = from_float<T>(g * s * (u + shift));
+  }
+}
+
+DLLM_EXPORT int dllm_glu_clamped(void* out, const void* in, int rows, int width, float limit, float alpha, float shift,
+                                 int dtype, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (width <= 0 || out == nullptr || in == nullptr) return DLLM_BAD_ARGUMENT;
+  long long total = (long long)rows * width;
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == DLLM_F32)
+    return dllm_launch_pdl(glu_clamped_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out,
+                           (const float*)in, total, width, limit, alpha, shift);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(glu_clamped_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                           (const __nv_bfloat16*)in, total, width, limit, alpha, shift);
+  return DLLM_BAD_ARGUMENT;
+}
+
+// ---- sum of RMS-normed branches into the residual ----------------------------------------------------------------
+// residual[r] += factor * (a[r] / rms(a[r]) * wa + b[r] / rms(b[r]) * wb), everything float32; one block per row.
+__global__ void norm_sum_residual_kernel(float* __restrict__ residual, const float* __restrict__ a,
+                                         const float* __restrict__ wa, const float* __restrict__ b,
+                                         const float* __restrict__ wb, int hidden, float eps, float factor) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t base = (size_t)blockIdx.x * hidden;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float va = a[base + i], vb = b[base + i];
+    sa = fmaf(va, va, sa);
+    sb = fmaf(vb, vb, sb);
+  }
+  float inv_a = 1.0f / sqrtf(block_sum(sa, scratch) / (float)hidden + eps);
+  float inv_b = 1.0f / sqrtf(block_sum(sb, scratch) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    residual[base + i] += factor * (a[base + i] * inv_a * wa[i] + b[base + i] * inv_b * wb[i]);
+}
+
+DLLM_EXPORT int dllm_norm_sum_residual(float* residual, const float* a, const float* wa, const float* b, const float* wb,
+                                       int rows, int hidden, float eps, float factor, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (hidden <= 0) return DLLM_BAD_ARGUMENT;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  return dllm_launch_pdl(norm_sum_residual_kernel, dim3(rows), dim3(threads), 0, stream, residual, a, wa, b, wb, hidden,
+                         eps, factor);
+}
+
+// ---- the stream beside a kept copy, as one operand ---------------------------------------------------------------
+// both[r] = [x[r] | kept[r]] in the activation type (the operand of the product that mixes the two), and then
+// x[r] = start (one row for all): the product adds into x in its epilogue, so x ends as start + W [x | kept].
+template <typename T>
+__global__ void concat_restart_kernel(T* __restrict__ both, float* __restrict__ x, const float* __restrict__ kept,
+                                      const float* __restrict__ start, long long total, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i / hidden;
+    int c = (int)(i - r * hidden);
+    both[r * 2 * hidden + c] = from_float<T>(x[i]);
+    both[r * 2 * hidden + hidden + c] = from_float<T>(kept[i]);
+    x[i] = start != nullptr ? start[c] : 0.f;
+  }
+}
+
+DLLM_EXPORT int dllm_concat_restart(void* both, float* x, const float* kept, const float* start, int rows, int hidden,
+                                    int dtype, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (hidden <= 0 || both == nullptr || x == nullptr || kept == nullptr) return DLLM_BAD_ARGUMENT;
+  long long total = (long long)rows * hidden;
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == DLLM_F32)
+    return dllm_launch_pdl(concat_restart_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)both, x, kept,
+                           start, total, hidden);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(concat_restart_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                           (__nv_bfloat16*)both, x, kept, start, total, hidden);
+  return DLLM_BAD_ARGUMENT;
 }

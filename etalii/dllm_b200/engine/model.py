@@ -37,6 +37,8 @@ class Model:
             roles = layer.roles()
             layer_parts.append({name: build(f"layers.{index}.{name}", roles[name], part_spec)
                                 for name, part_spec in layer.parts.items()})
+        self.reentries = [build(f"reentries.{index}", "reentry", part_spec)
+                          for index, part_spec in enumerate(spec.reentries)]
         self.final_norm = build("final_norm", "norm", spec.final_norm)
         self.head = build("head", "head", spec.head)
         refused = []
@@ -54,7 +56,7 @@ class Model:
             from ..kernels.build import prebuild
 
             names = {"elementwise", "gemm_simt" if rt.dtype == torch.float32 else "gemv"}
-            for part in self._layer_parts():
+            for part in (*self._layer_parts(), *self.reentries):
                 if hasattr(part, "kernel_libraries"):
                     names |= set(part.kernel_libraries(rt))
             prebuild(sorted(names))
@@ -66,17 +68,28 @@ class Model:
             if entry.writes_cache:
                 mixer = self.blocks[entry.layer].mixer
                 needs[entry.cache] = mixer.cache_need() if hasattr(mixer, "cache_need") else None
+        # A mixer that keeps several things (kind "several") gets a cache entry for each, numbered behind the
+        # schedule's own; its view is the tuple of their views, in the order it listed them.
+        several: dict[int, list[int]] = {}
+        index = 0
+        while index < len(needs):  # (a part may itself keep several things: the list grows as it is walked)
+            if needs[index] is not None and needs[index].kind == "several":
+                several[index] = list(range(len(needs), len(needs) + len(needs[index].parts)))
+                needs.extend(needs[index].parts)
+                needs[index] = None
+            index += 1
         self.cache = PagedCache(needs, max_tokens=max_tokens, max_length=rt.max_length, dtype=rt.dtype,
                                 device=rt.device, page_size=page_size, max_slots=max_slots)
-        self._views = []
-        for entry in self.order:
-            need = needs[entry.cache]
+
+        def view_of(index):
+            if index in several:
+                return tuple(view_of(part) for part in several[index])
+            need = needs[index]
             if need is None:
-                self._views.append(None)
-            elif need.kind == "kv":
-                self._views.append(self.cache.kv_view(entry.cache))
-            else:
-                self._views.append(self.cache.state(entry.cache))
+                return None
+            return self.cache.kv_view(index) if need.kind == "kv" else self.cache.state(index)
+
+        self._views = [view_of(entry.cache) for entry in self.order]
 
         self._plan_prefetch()
         # the C++ host side of prefill-sized steps, for models made of the parts it restates (else None)
@@ -100,7 +113,7 @@ class Model:
     def capturable(self) -> bool:
         """Whether a decode step of this model can be captured in a CUDA graph: every block and part may say no
         (`CAPTURABLE = False`, e.g. a part written with allocating torch ops); the library's own all can."""
-        things = [*self.blocks, *self._layer_parts(), self.embedding, self.final_norm, self.head]
+        things = [*self.blocks, *self._layer_parts(), *self.reentries, self.embedding, self.final_norm, self.head]
         return all(getattr(thing, "CAPTURABLE", True) for thing in things)
 
     def _plan_prefetch(self, ahead: int = 4) -> None:
@@ -140,7 +153,13 @@ class Model:
         if self.native_layers is not None and self.native_layers.takes(batch):
             self.native_layers.run(x, batch, rt)  # every layer's launches from one C++ call
         else:
+            embedded = None
+            if self.reentries:  # the embedding's output is kept for the parts that mix it back in
+                embedded = rt.ws.buffer("embedded", tuple(x.shape), torch.float32)
+                embedded.copy_(x)
             for entry, view in zip(self.order, self._views):
+                if entry.reentry is not None:
+                    self.reentries[entry.reentry].forward(x, embedded, entry.round, batch, rt)
                 self.blocks[entry.layer].forward(x, batch, view, rt, entry.writes_cache)
         if batch.n_want == 0:
             return None

@@ -35,6 +35,7 @@ SOURCES = {
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tcgen05": "attention_prefill_tcgen05.cu",
     "attention_decode_static": "attention_decode_static.cu",
+    "recurrent": "recurrent.cu",
     "sampling": "sampling.cu",
     "step_launcher": "step_launcher.cu",
 }

@@ -22,7 +22,23 @@ class KernelError(RuntimeError):
 
 _prototypes = {
     ("elementwise", "dllm_embed"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("elementwise", "dllm_embed_scaled"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                           c_void_p],
     ("elementwise", "dllm_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    ("elementwise", "dllm_layernorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    ("elementwise", "dllm_glu_clamped"): [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
+    ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                                c_float, c_void_p],
+    ("elementwise", "dllm_concat_restart"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("recurrent", "dllm_decay_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                       c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    ("recurrent", "dllm_delta_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    ("recurrent", "dllm_delta_prepare"): [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_int, c_void_p],
+    ("recurrent", "dllm_gated_norm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                       c_int, c_int, c_void_p],
     ("elementwise", "dllm_rope_cache_write"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                c_int, c_int, c_longlong, c_void_p],
@@ -150,8 +166,9 @@ def _code(dtype: torch.dtype) -> int:
         raise KernelError(f"dtype {dtype} is not supported (float32 and bfloat16 are)") from None
 
 
-def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor | None = None) -> None:
-    """out[r] = float32(table[tokens[r]]); a token outside the table gives a zero row and sets the status word
+def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor | None = None,
+          scale: float = 1.0) -> None:
+    """out[r] = float32(table[tokens[r]]) * scale; a token outside the table gives a zero row and sets the status word
     (`status`: an int32 word the device can write; default: the pinned word that `raise_if_failed` reads)."""
     _cuda(out, table, tokens)
     if status is None:
@@ -159,9 +176,9 @@ def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: 
     assert out.dtype == torch.float32 and tokens.dtype == torch.int32 and status.dtype == torch.int32
     rows, hidden = out.shape
     assert tokens.numel() >= rows and table.shape[1] == hidden
-    _check(_fn("elementwise", "dllm_embed")(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), rows, hidden,
-                                            table.shape[0], _code(table.dtype), status.data_ptr(), _stream()),
-           "embed")
+    _check(_fn("elementwise", "dllm_embed_scaled")(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), rows, hidden,
+                                                   table.shape[0], _code(table.dtype), float(scale),
+                                                   status.data_ptr(), _stream()), "embed")
 
 
 def copy_to_device(dst_ptr: int, src_ptr: int, nbytes: int) -> None:
@@ -183,6 +200,133 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float
     _check(_fn("elementwise", "dllm_rmsnorm")(out.data_ptr(), x.data_ptr(), weight.data_ptr(),
                                               rows.data_ptr() if rows is not None else None, n, x.shape[-1],
                                               float(eps), _code(out.dtype), _stream()), "rmsnorm")
+
+
+def layernorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float,
+              rows: torch.Tensor | None = None) -> None:
+    """out[r] = (x - mean) / sqrt(variance + eps) * weight of row r (or of row rows[r]); x and weight float32, the
+    variance the mean of the squared deviations."""
+    _cuda(out, x, weight, rows)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == x.shape[-1]
+    n = out.shape[0]
+    assert out.shape[-1] == x.shape[-1] and (rows is not None or x.shape[0] >= n)
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n)
+    _check(_fn("elementwise", "dllm_layernorm")(out.data_ptr(), x.data_ptr(), weight.data_ptr(),
+                                                rows.data_ptr() if rows is not None else None, n, x.shape[-1],
+                                                float(eps), _code(out.dtype), _stream()), "layernorm")
+
+
+def glu_clamped(out: torch.Tensor, gate_up: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
+    """gate_up [rows, 2 width] = [gate | up]; out[rows, width] = g sigmoid(alpha g) (u + shift) with g = min(gate,
+    limit), u = clamp(up, -limit, limit), in float32, rounded once."""
+    _cuda(out, gate_up)
+    rows, width = out.shape
+    assert gate_up.shape == (rows, 2 * width) and gate_up.dtype == out.dtype
+    _check(_fn("elementwise", "dllm_glu_clamped")(out.data_ptr(), gate_up.data_ptr(), rows, width, float(limit),
+                                                  float(alpha), float(shift), _code(out.dtype), _stream()),
+           "glu_clamped")
+
+
+def norm_sum_residual(residual: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor,
+                      eps: float, factor: float) -> None:
+    """residual += factor * (a / rms(a) * wa + b / rms(b) * wb), row by row, all float32."""
+    _cuda(residual, a, wa, b, wb)
+    rows, hidden = a.shape
+    assert all(t.dtype == torch.float32 for t in (residual, a, wa, b, wb))
+    assert b.shape == a.shape and residual.shape[0] >= rows and residual.shape[1] == hidden
+    assert wa.numel() == hidden and wb.numel() == hidden
+    _check(_fn("elementwise", "dllm_norm_sum_residual")(residual.data_ptr(), a.data_ptr(), wa.data_ptr(), b.data_ptr(),
+                                                        wb.data_ptr(), rows, hidden, float(eps), float(factor),
+                                                        _stream()), "norm_sum_residual")
+
+
+def concat_restart(both: torch.Tensor, x: torch.Tensor, kept: torch.Tensor, start: torch.Tensor | None) -> None:
+    """both[r] = [x[r] | kept[r]] in both's dtype, then x[r] = start (a row of float32, or zeros)."""
+    _cuda(both, x, kept, start)
+    rows, hidden = kept.shape
+    assert x.dtype == torch.float32 and kept.dtype == torch.float32 and x.shape == kept.shape
+    assert both.shape == (rows, 2 * hidden) and (start is None or (start.dtype == torch.float32 and
+                                                                    start.numel() == hidden))
+    _check(_fn("elementwise", "dllm_concat_restart")(both.data_ptr(), x.data_ptr(), kept.data_ptr(),
+                                                     start.data_ptr() if start is not None else None, rows, hidden,
+                                                     _code(both.dtype), _stream()), "concat_restart")
+
+
+def _columns(rows: torch.Tensor, offset: int) -> int:
+    return rows.data_ptr() + 4 * int(offset)
+
+
+def decay_scan(out: torch.Tensor, rows: torch.Tensor, q_at: int, k_at: int, v_at: int, heads: int, dim: int, vdim: int,
+               decay: torch.Tensor, silu_inputs: bool, k_scale: float, state: torch.Tensor, batch) -> None:
+    """Per sequence and head, over the step's tokens in order: S <- decay_h S + k v^T, out = S^T q, from and to
+    `state` [slots, heads, vdim, dim] (float32, S stored column by column). `rows` [tokens, n] float32 holds q, k
+    and v of a token at the column offsets q_at, k_at, v_at; with `silu_inputs` they pass silu first; k is multiplied
+    by k_scale."""
+    _cuda(out, rows, decay, state)
+    assert rows.dtype == torch.float32 and out.dtype == torch.float32 and state.dtype == torch.float32
+    assert decay.dtype == torch.float32 and decay.numel() == heads
+    assert tuple(state.shape[1:]) == (heads, vdim, dim) and out.shape[1] == heads * vdim
+    assert rows.shape[0] >= batch.n_tokens and out.shape[0] >= batch.n_tokens
+    _check(_fn("recurrent", "dllm_decay_scan")(
+        _columns(rows, q_at), _columns(rows, k_at), _columns(rows, v_at), rows.shape[1], heads, dim, vdim,
+        decay.data_ptr(), 1 if silu_inputs else 0, float(k_scale), state.data_ptr(), batch.cu_seqlens.data_ptr(),
+        batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(), _stream()), "decay_scan",
+        lambda: f"dim={dim} (a multiple of 4, at most 256)")
+
+
+def delta_prepare(prepared: torch.Tensor, aux: torch.Tensor, rows: torch.Tensor, b_at: int, a_at: int,
+                  taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, history: torch.Tensor | None,
+                  heads: int, qk_heads: int, dim: int, vdim: int, batch) -> None:
+    """What the gated delta rule's scan reads, from the projected rows [tokens, n] float32 = [q | k | v | ...]:
+    the causal convolution over time per channel (taps [channels, width] float32; inputs of earlier steps from
+    `history` [slots, width - 1, channels], which is moved on), silu, unit vectors for q and k per head (q times
+    dim^-1/2) -> prepared [tokens, channels]; and aux [tokens, 2 heads + qk_heads] = decay g, step size beta (from
+    the columns at a_at and b_at), and k.q."""
+    _cuda(prepared, aux, rows, taps, a_log, dt_bias, history)
+    channels = 2 * qk_heads * dim + heads * vdim
+    assert all(t.dtype == torch.float32 for t in (prepared, aux, rows, taps, a_log, dt_bias))
+    assert taps.shape[0] == channels and prepared.shape[1] == channels and aux.shape[1] == 2 * heads + qk_heads
+    width = taps.shape[1]
+    assert history is None or (history.dtype == torch.float32 and tuple(history.shape[1:]) == (width - 1, channels))
+    _check(_fn("recurrent", "dllm_delta_prepare")(
+        rows.data_ptr(), rows.shape[1], int(b_at), int(a_at), taps.data_ptr(), width, a_log.data_ptr(),
+        dt_bias.data_ptr(), history.data_ptr() if history is not None else None, batch.tok_seq.data_ptr(),
+        batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), batch.n_tokens, batch.n_seqs, heads, qk_heads, dim, vdim,
+        prepared.data_ptr(), aux.data_ptr(), 1 if batch.is_decode else 0, _stream()), "delta_prepare",
+        lambda: f"taps={width} (at most 8), dim={dim} (a multiple of 4, at most 256)")
+    if not batch.is_decode and width > 1:
+        global launches
+        launches += 1  # (the history's own small kernel)
+
+
+def delta_scan(out: torch.Tensor, prepared: torch.Tensor, aux: torch.Tensor, heads: int, qk_heads: int, dim: int,
+               vdim: int, state: torch.Tensor, batch) -> None:
+    """Per sequence and head, over the step's tokens in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    out = S^T q, from and to `state` [slots, heads, vdim, dim]. `prepared`, `aux`: what `delta_prepare` wrote."""
+    _cuda(out, prepared, aux, state)
+    assert all(t.dtype == torch.float32 for t in (out, prepared, aux, state))
+    assert tuple(state.shape[1:]) == (heads, vdim, dim) and out.shape[1] == heads * vdim
+    _check(_fn("recurrent", "dllm_delta_scan")(
+        prepared.data_ptr(), _columns(prepared, qk_heads * dim), _columns(prepared, 2 * qk_heads * dim),
+        prepared.shape[1], heads, qk_heads, dim, vdim, aux.data_ptr(), aux.shape[1], state.data_ptr(),
+        batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(), _stream()), "delta_scan",
+        lambda: f"dim={dim} (a multiple of 4, at most 256)")
+
+
+GATE_SILU, GATE_SIGMOID = 1, 2
+
+
+def gated_norm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor | None, rows: torch.Tensor, gate_at: int,
+               group: int, eps: float, gate: int) -> None:
+    """out = x / rms(x over groups of `group` values) * weight[i % group] * gate(z), z the token's gate values at
+    column offset gate_at of `rows` [tokens, n] float32; gate GATE_SILU or GATE_SIGMOID. x float32 [tokens, width]."""
+    _cuda(out, x, weight, rows)
+    tokens, width = out.shape
+    assert x.dtype == torch.float32 and rows.dtype == torch.float32 and x.shape[1] == width
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == group)
+    _check(_fn("recurrent", "dllm_gated_norm")(
+        out.data_ptr(), x.data_ptr(), weight.data_ptr() if weight is not None else None, _columns(rows, gate_at),
+        rows.shape[1], tokens, width, int(group), float(eps), int(gate), _code(out.dtype), _stream()), "gated_norm")
 
 
 prefetch_hints: dict[int, torch.Tensor] = {}

@@ -38,7 +38,12 @@ class Attention:
     accepts_pending_norm = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                 window: int | None = None, position=None) -> None:
+                 window: int | None = None, position=None, values: str = "projected") -> None:
+        """`values`: "projected" has a value matrix of its own; "keys" has none: a token's values are its keys as
+        projected, before the rotation (the key matrix's rows serve twice in the fused projection)."""
+        if values not in ("projected", "keys"):
+            raise ValueError(f"values {values!r}: projected or keys")
+        self.values = values
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
@@ -48,10 +53,13 @@ class Attention:
         self.w_qkv = self.w_o = None
 
     @staticmethod
-    def parameters(hidden_size, num_heads, num_kv_heads, head_dim, **_) -> dict[str, ParamSpec]:
+    def parameters(hidden_size, num_heads, num_kv_heads, head_dim, values="projected", **_) -> dict[str, ParamSpec]:
         q, kv = int(num_heads) * int(head_dim), int(num_kv_heads) * int(head_dim)
-        return {"q": ParamSpec((q, hidden_size)), "k": ParamSpec((kv, hidden_size)),
-                "v": ParamSpec((kv, hidden_size)), "o": ParamSpec((hidden_size, q))}
+        out = {"q": ParamSpec((q, hidden_size)), "k": ParamSpec((kv, hidden_size)),
+               "v": ParamSpec((kv, hidden_size)), "o": ParamSpec((hidden_size, q))}
+        if values == "keys":
+            del out["v"]
+        return out
 
     def supports(self, rt) -> str | None:
         """None, or why the attention kernels cannot run these sizes (asked before weights go to the device)."""
@@ -68,9 +76,25 @@ class Attention:
 
     def bind(self, tensors, rt) -> None:
         # one projection for q, k and v: the rows of the three matrices one after another
-        fused = torch.cat([tensors["q"].to(rt.dtype), tensors["k"].to(rt.dtype), tensors["v"].to(rt.dtype)], dim=0)
+        q, k = tensors["q"].to(rt.dtype), tensors["k"].to(rt.dtype)
+        v = k if self.values == "keys" else tensors["v"].to(rt.dtype)
+        o = tensors["o"]
+        order = self.position.row_order() if self.position is not None and hasattr(self.position, "row_order") \
+            else None
+        if order is not None:
+            # The position encoding pairs other dimensions than the kernels rotate: every head's dimensions are
+            # put in the kernels' order, in q and k alike (no q . k changes). Values that are the keys come out of
+            # attention in that order too, so the output matrix's columns follow.
+            index = torch.tensor(order, dtype=torch.long)
+            q = q.view(self.num_heads, self.head_dim, -1)[:, index].reshape(q.shape)
+            k = k.view(self.num_kv_heads, self.head_dim, -1)[:, index].reshape(k.shape)
+            if self.values == "keys":
+                v = k
+                o = o.view(o.shape[0], self.num_heads, self.head_dim)[:, :, index].reshape(o.shape)
+        fused = torch.cat([q, k, v], dim=0)
         self.w_qkv = fused.contiguous().to(rt.device)
-        self.w_o = rt.to_device(tensors["o"], rt.dtype)
+        self.w_o = o.to(rt.dtype).contiguous().to(rt.device) if o is not tensors["o"] else \
+            rt.to_device(tensors["o"], rt.dtype)
         if self.position is not None:
             self.position.bind({}, rt)
 
@@ -82,8 +106,11 @@ class Attention:
         self.w_qkv = (self.w_qkv.float() * scale.to(self.w_qkv.device).float()[None, :]).to(torch.bfloat16).contiguous()
         return True
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True) -> None:
-        """h: normed activations [tokens, hidden]; adds the attention output to `residual` (float32) in place."""
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True,
+                epilogue: int = ops.EPI_RESIDUAL) -> None:
+        """h: normed activations [tokens, hidden]; adds the attention output to `residual` (float32) in place. A
+        mixer that runs this one as a branch passes `epilogue=ops.EPI_STORE_F32`: `residual` is then its buffer for
+        the branch's output and is overwritten."""
         n = batch.n_tokens
         q_size = self.num_heads * self.head_dim
         q = rt.ws.buffer("q", (n, q_size), rt.dtype)
@@ -137,7 +164,7 @@ class Attention:
             ops.attention_blocks(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         else:
             ops.attention_general(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
-        ops.gemm(residual, attended, self.w_o, ops.EPI_RESIDUAL)
+        ops.gemm(residual, attended, self.w_o, epilogue)
 
 
     def kernel_libraries(self, rt) -> set[str]:

@@ -34,4 +34,20 @@ class PreNormBlock:
         self.feed_forward.forward(normed(self.feed_forward_norm, self.feed_forward, x, rt), x, batch, rt)
 
 
+class PreNormMixerBlock:
+    """A layer without a feed-forward: x += mixer(norm(x))."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    def __init__(self, mixer, mixer_norm) -> None:
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.parts = {"mixer": mixer, "mixer_norm": mixer_norm}
+        if hasattr(mixer_norm, "give_weight_to"):
+            mixer_norm.give_weight_to(mixer)
+
+    def forward(self, x, batch, cache, rt, write_cache: bool = True) -> None:
+        self.mixer.forward(normed(self.mixer_norm, self.mixer, x, rt), x, batch, cache, rt, write_cache)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "pre_norm_mixer", PreNormMixerBlock)

@@ -12,12 +12,13 @@ from .spec import ParamSpec
 
 
 class TokenEmbedding:
-    def __init__(self, vocab_size: int, hidden_size: int) -> None:
-        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0) -> None:
+        """`scale`: every embedding row is multiplied by it on the way into the stream (in float32)."""
+        self.vocab_size, self.hidden_size, self.scale = int(vocab_size), int(hidden_size), float(scale)
         self.weight = None
 
     @staticmethod
-    def parameters(vocab_size, hidden_size) -> dict[str, ParamSpec]:
+    def parameters(vocab_size, hidden_size, **_) -> dict[str, ParamSpec]:
         return {"weight": ParamSpec((vocab_size, hidden_size))}
 
     def bind(self, tensors, rt) -> None:
@@ -27,7 +28,7 @@ class TokenEmbedding:
         # a token outside the table sets the kernels' shared status word, which the engine looks at after each
         # step it waits for (kernels/ops.py::raise_if_failed)
         x = rt.ws.buffer("residual", (n_tokens, self.hidden_size), torch.float32)
-        ops.embed(x, self.weight, tokens)
+        ops.embed(x, self.weight, tokens, scale=self.scale)
         return x
 
 

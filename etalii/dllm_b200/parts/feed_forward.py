@@ -70,4 +70,45 @@ class SwiGLU:
         return names
 
 
+class ClampedGLU:
+    """A gated feed-forward whose pre-activations are clamped: g = min(gate(h), limit), u = clamp(up(h), -limit,
+    limit); down(g * sigmoid(alpha * g) * (u + shift)). Gate and up are one product ([gate rows | up rows]); the
+    activation is a kernel of its own between the two products, computed in float32."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
+                 shift: float = 1.0) -> None:
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.w_gate_up = self.w_down = None
+
+    @staticmethod
+    def parameters(hidden_size, intermediate_size, **_) -> dict[str, ParamSpec]:
+        return {"gate": ParamSpec((intermediate_size, hidden_size)), "up": ParamSpec((intermediate_size, hidden_size)),
+                "down": ParamSpec((hidden_size, intermediate_size))}
+
+    def supports(self, rt) -> str | None:
+        return row_rule(rt, hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
+
+    def bind(self, tensors, rt) -> None:
+        fused = torch.cat([tensors["gate"].to(rt.dtype), tensors["up"].to(rt.dtype)], dim=0)
+        self.w_gate_up = fused.contiguous().to(rt.device)
+        self.w_down = rt.to_device(tensors["down"], rt.dtype)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt) -> None:
+        if isinstance(h, NormedInput):
+            h = h.tensor()
+        rows = h.shape[0]
+        both = rt.ws.buffer("ffn_gate_up", (rows, 2 * self.intermediate_size), rt.dtype)
+        ops.gemm(both, h, self.w_gate_up, ops.EPI_STORE_T)
+        act = rt.ws.buffer("ffn_act", (rows, self.intermediate_size), rt.dtype)
+        ops.glu_clamped(act, both, self.limit, self.alpha, self.shift)
+        ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
+
+    def kernel_libraries(self, rt) -> set[str]:
+        if rt.dtype != torch.bfloat16:
+            return {"gemm_simt", "elementwise"}
+        return {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise"}
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "clamped_glu", ClampedGLU)

@@ -65,6 +65,30 @@ class RMSNorm:
         return NormedInput(self, x, rt)
 
 
+class LayerNorm:
+    """Layer norm with a weight and no bias: out = (x - mean) / sqrt(variance + eps) * weight, the variance being the
+    mean of the squared deviations; computed in float32 from the float32 residual stream. It is never folded into a
+    product (the mean would have to go through the product as well), so its consumers get the normed rows."""
+
+    def __init__(self, hidden_size: int, eps: float) -> None:
+        self.hidden_size, self.eps = int(hidden_size), float(eps)
+        self.weight = None
+
+    @staticmethod
+    def parameters(hidden_size: int, eps: float) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((int(hidden_size),), "ones")}
+
+    def bind(self, tensors, rt) -> None:
+        self.weight = rt.to_device(tensors["weight"], torch.float32)
+
+    def forward(self, x: torch.Tensor, rt, rows: torch.Tensor | None = None, n_rows: int | None = None,
+                name: str = "normed") -> torch.Tensor:
+        n = x.shape[0] if rows is None else int(n_rows)
+        out = rt.ws.buffer(name, (n, self.hidden_size), rt.dtype)
+        ops.layernorm(out, x, self.weight, self.eps, rows)
+        return out
+
+
 FUSE_NORM_LIMIT = 16 << 20
 """Weights up to this many bytes take the norm inside their decode-sized product (one kernel less); with larger
 weights every block of the product would redo the norm of all rows, and a separate norm kernel is cheaper."""
@@ -97,3 +121,4 @@ def project(out: torch.Tensor, h, w: torch.Tensor, epilogue: int) -> None:
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

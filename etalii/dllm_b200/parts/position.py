@@ -44,7 +44,13 @@ class RotaryEmbedding:
     rotation)."""
 
     def __init__(self, head_dim: int, theta: float, scaling: Mapping | None = None,
-                 rotary_dim: int | None = None) -> None:
+                 rotary_dim: int | None = None, pairing: str = "halves") -> None:
+        """`pairing`: which dimensions of a head turn together. "halves": i with i + rotary_dim / 2; "interleaved":
+        2i with 2i + 1. The kernels rotate halves; a mixer brings another pairing into that layout by reordering
+        the rows of its q and k matrices once, at load time (`row_order`), which changes no q . k."""
+        if pairing not in ("halves", "interleaved"):
+            raise ValueError(f"rotary pairing {pairing!r} is not known (halves, interleaved)")
+        self.pairing = pairing
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim) if rotary_dim else self.head_dim
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
@@ -70,6 +76,16 @@ class RotaryEmbedding:
 
     def table(self) -> torch.Tensor | None:
         return self._table
+
+    def row_order(self) -> list[int] | None:
+        """For each place of a head as the kernels see it, the dimension of the model's head that belongs there (None:
+        they are the same). Pair i of an interleaved head, dimensions (2i, 2i + 1), goes to the places
+        (i, i + rotary_dim / 2); dimensions beyond rotary_dim stay."""
+        if self.pairing == "halves":
+            return None
+        half = self.rotary_dim // 2
+        return [2 * i for i in range(half)] + [2 * i + 1 for i in range(half)] + \
+            list(range(self.rotary_dim, self.head_dim))
 
 
 register_part("position", "rotary", RotaryEmbedding)

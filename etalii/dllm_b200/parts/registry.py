@@ -1,10 +1,10 @@
 """Registries of part kinds. A part class is registered under a role ("norm", "position", "mixer", "feed_forward",
-"block", "embedding", "head") and a kind name; `build_part` makes an instance from a `PartSpec`."""
+"block", "embedding", "head", "reentry") and a kind name; `build_part` makes an instance from a `PartSpec`."""
 from __future__ import annotations
 
 from typing import Any, Callable
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "reentry")
 _PARTS: dict[str, dict[str, Callable[..., Any]]] = {role: {} for role in ROLES}
 
 

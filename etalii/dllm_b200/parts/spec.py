@@ -71,6 +71,10 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    reentry: int | None = None
+    """Index into `ModelSpec.reentries` of a part that rewrites the stream right before this run (None: nothing)."""
+    round: int = 0
+    """Which round of a repeated stretch of layers this run belongs to; the reentry part is told."""
 
 
 @dataclass(frozen=True)
@@ -84,6 +88,9 @@ class ModelSpec:
     head: PartSpec
     schedule: tuple[ScheduleEntry, ...] = ()
     """Empty means every layer once, in order, each with a cache of its own."""
+    reentries: tuple[PartSpec, ...] = ()
+    """Parts of role "reentry": each rewrites the stream between two runs of the schedule from the stream itself and
+    the embedding's output (`forward(x, embedded, round, batch, rt)`); schedule entries name them by index."""
     stop_token_ids: tuple[int, ...] = ()
     equal_if_present: Mapping[str, str] = field(default_factory=dict)
     """Checkpoint tensors that may be present although the model does not use them, and must then equal another
@@ -102,5 +109,6 @@ class ModelSpec:
         for index, layer in enumerate(self.layers):
             roles = layer.roles()
             out += [(f"layers.{index}.{name}", roles[name], spec) for name, spec in layer.parts.items()]
+        out += [(f"reentries.{index}", "reentry", spec) for index, spec in enumerate(self.reentries)]
         out += [("final_norm", "norm", self.final_norm), ("head", "head", self.head)]
         return out
