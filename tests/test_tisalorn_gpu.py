@@ -1,0 +1,488 @@
+"""Tisalorn on the GPU against the plain implementation (tests/plain_tisalorn.py): every mechanism alone through its
+part, then whole models through the engine's step function, decode graph and generation loop, cut and batched in
+every way a server would."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_tisalorn as P
+import tisalorn_cases as C
+from helpers import TOL, host, rel_error
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [("float32", torch.float32), ("bfloat16", torch.bfloat16)]
+PART_TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+def _runtime(dtype, max_length=512):
+    from etalii.dllm_b200.engine.runtime import Runtime
+
+    return Runtime(DEV, dtype, max_length)
+
+
+def _f64(weights):
+    return {k: v.to(P.F64) for k, v in weights.items()}
+
+
+def _bf16(generator, rows, cols, gain=1.0):
+    return (torch.randn(rows, cols, generator=generator) * gain / math.sqrt(cols)).to(torch.bfloat16)
+
+
+class PartHarness:
+    """A mixer part with a cache of its own and sequences that are fed in pieces."""
+
+    def __init__(self, part, dtype, sequences):
+        from etalii.dllm_b200.cache.paged import PagedCache
+        from etalii.dllm_b200.engine.batch import BatchBuffers
+
+        need = part.cache_need()
+        flat = list(need.parts) if need.kind == "several" else [need]
+        self.cache = PagedCache(flat, 64 * 24, 512, dtype=dtype, device=DEV)
+        views = [self.cache.kv_view(i) if n.kind == "kv" else self.cache.state(i) for i, n in enumerate(flat)]
+        self.view = tuple(views) if need.kind == "several" else views[0]
+        self.part, self.buffers = part, BatchBuffers(DEV)
+        self.slots = self.cache.acquire(sequences)
+
+    def step(self, rt, which, pieces, width):
+        """pieces[i]: the next rows [n_i, hidden] of sequence which[i]; returns the mixer's output rows per piece."""
+        slots = [self.slots[i] for i in which]
+        starts = []
+        for slot, piece in zip(slots, pieces):
+            self.cache.reserve(slot, piece.shape[0])
+            starts.append(self.cache.length(slot))
+        self.cache.sync_tables()
+        batch = self.buffers.fill(slots, [[0] * p.shape[0] for p in pieces], starts, [[] for _ in pieces])
+        h = torch.cat(pieces).to(rt.dtype).to(DEV).contiguous()
+        residual = torch.zeros(h.shape[0], width, device=DEV)
+        self.part.forward(h, residual, batch, self.view, rt)
+        for slot, piece in zip(slots, pieces):
+            self.cache.advance(slot, piece.shape[0])
+        out, at = [], 0
+        for piece in pieces:
+            out.append(host(residual[at:at + piece.shape[0]]))
+            at += piece.shape[0]
+        return out
+
+
+def _feed(harness, rt, sequences, schedule, width):
+    """Feeds `sequences` (tensors [n, hidden]) by `schedule`: a list of steps, each a list of (sequence, count)."""
+    at = [0] * len(sequences)
+    got = [[] for _ in sequences]
+    for step in schedule:
+        which = [i for i, _ in step]
+        pieces = [sequences[i][at[i]:at[i] + n] for i, n in step]
+        for (i, n), rows in zip(step, harness.step(rt, which, pieces, width)):
+            got[i].append(rows)
+            at[i] += n
+    assert all(a == s.shape[0] for a, s in zip(at, sequences))
+    return [np.concatenate(g) for g in got]
+
+
+SCHEDULE = [[(0, 70), (1, 2), (2, 17)], [(0, 1), (1, 1), (2, 1)], [(0, 1), (1, 1), (2, 1)], [(0, 2), (2, 65)],
+            [(0, 1), (2, 1)], [(2, 1)]]
+LENGTHS = [75, 4, 86]
+
+
+def _inputs(dtype, width, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(n, width, generator=g).to(dtype).float() for n in LENGTHS]
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000])
+def test_layer_norm_part(name, dtype, width):
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    norm = build_part("norm", PartSpec("layernorm", {"hidden_size": width, "eps": 3e-4}))
+    w = torch.randn(width) * 0.1 + 1
+    norm.bind({"weight": w}, rt)
+    x = torch.randn(11, width, device=DEV) * 2 + 0.7  # a mean that is not zero
+    want = P.layer_norm(x.cpu().to(P.F64), w.to(P.F64), 3e-4).numpy()
+    assert rel_error(host(norm.forward(x, rt)), want) <= (2e-6 if dtype == torch.float32 else 8e-3)
+    rows = torch.tensor([9, 0, 4], dtype=torch.int32, device=DEV)
+    got = host(norm.forward(x, rt, rows=rows, n_rows=3, name="picked"))
+    assert rel_error(got, want[[9, 0, 4]]) <= (2e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+@pytest.mark.parametrize("rows", [3, 40, 150])
+def test_clamped_glu_part(name, dtype, rows):
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    part = build_part("feed_forward", PartSpec("clamped_glu", {"hidden_size": 72, "intermediate_size": 200,
+                                                               "limit": 0.9}))
+    g = torch.Generator().manual_seed(2)
+    weights = {"gate": _bf16(g, 200, 72, 1.5), "up": _bf16(g, 200, 72, 1.5), "down": _bf16(g, 72, 200)}
+    part.bind(weights, rt)
+    h = torch.randn(rows, 72, generator=g).to(dtype)
+    residual = torch.ones(rows, 72, device=DEV)
+    part.forward(h.to(DEV), residual, None, rt)
+    pre = h.to(P.F64) @ weights["gate"].to(P.F64).T
+    assert (pre > 0.9).any() and (pre < -0.9).any()  # the clamp is at work on both sides
+    want = 1 + P.clamped_glu(_f64(weights), {"limit": 0.9}, h.to(P.F64)).numpy()
+    assert rel_error(host(residual), want) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+def test_scaled_embedding_and_reentry_parts(name, dtype):
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    g = torch.Generator().manual_seed(4)
+    table = _bf16(g, 50, 40, 6.0)
+    embedding = build_part("embedding", PartSpec("token_embedding", {"vocab_size": 50, "hidden_size": 40,
+                                                                     "scale": 1.37}))
+    embedding.bind({"weight": table}, rt)
+    tokens = torch.tensor([3, 49, 0, 3, 17], dtype=torch.int32, device=DEV)
+    x = embedding.forward(tokens, 5, rt)
+    want = table.to(P.F64)[tokens.cpu().long()] * 1.37
+    assert rel_error(host(x), want.numpy()) <= 1e-6
+
+    reentry = build_part("reentry", PartSpec("concat_project", {"hidden_size": 40, "rounds": 3}))
+    weights = {"weight": _bf16(g, 40, 80, 1.4), "starts": torch.randn(3, 40, generator=g).to(torch.bfloat16)}
+    reentry.bind(weights, rt)
+
+    class Batch:
+        n_tokens = 5
+
+    stream = torch.randn(5, 40, generator=g).to(dtype).float()
+    kept = torch.randn(5, 40, generator=g).to(dtype).float()
+    for index in (0, 2):
+        x = stream.clone().to(DEV)
+        reentry.forward(x, kept.to(DEV), index, Batch, rt)
+        want = torch.cat([stream, kept], dim=1).to(P.F64) @ weights["weight"].to(P.F64).T \
+            + weights["starts"].to(P.F64)[index]
+        assert rel_error(host(x), want.numpy()) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+@pytest.mark.parametrize("kind", ["retention", "lightning"])
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 20, 8), (2, 64, 40), (1, 132, 16)])
+def test_decay_linear_attention_part(name, dtype, kind, heads, dim, vdim):
+    """Three sequences fed in unequal pieces (a prompt, single tokens, another portion of 2 and of 65, single tokens
+    again) against the plain recurrence over each whole sequence."""
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    width, eps = 56, 1e-5
+    decay = [1.0 - 2.0 ** -(3 + i) for i in range(heads)]
+    params = {"hidden_size": width, "heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "eps": eps}
+    if kind == "retention":
+        params.update(input_activation=None, key_scale=dim ** -0.5, norm="head", norm_weight=False, gate="silu")
+    else:
+        params.update(input_activation="silu", key_scale=1.0, norm="all", norm_weight=True, gate="sigmoid")
+    part = build_part("mixer", PartSpec("decay_linear_attention", params))
+    g = torch.Generator().manual_seed(7)
+    weights = {"q": _bf16(g, heads * dim, width, 1.5), "k": _bf16(g, heads * dim, width, 1.5),
+               "v": _bf16(g, heads * vdim, width, 1.5), "g": _bf16(g, heads * vdim, width, 1.5),
+               "o": _bf16(g, width, heads * vdim)}
+    if kind == "lightning":
+        weights["norm"] = (1 + 0.2 * torch.randn(heads * vdim, generator=g)).to(torch.bfloat16)
+    part.bind(weights, rt)
+    sequences = _inputs(dtype, width, 8)
+    got = _feed(PartHarness(part, dtype, 3), rt, sequences, SCHEDULE, width)
+    p = {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}
+    for rows, h in zip(got, sequences):
+        if kind == "retention":
+            want = P.retention(_f64(weights), p, h.to(P.F64), torch.zeros(heads, dim, vdim, dtype=P.F64), eps)
+        else:
+            want = P.lightning(_f64(weights), p, h.to(P.F64), {}, eps)
+        assert rel_error(rows, want.numpy()) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+@pytest.mark.parametrize("heads,qk_heads,dim,vdim,conv", [(4, 2, 16, 24, 3), (2, 2, 40, 16, 1), (6, 1, 64, 8, 5)])
+def test_gated_delta_rule_part(name, dtype, heads, qk_heads, dim, vdim, conv):
+    """The same pieces: portions shorter than the convolution reach back into the history the cache keeps."""
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    width, eps = 56, 1e-5
+    part = build_part("mixer", PartSpec("gated_delta_rule", {"hidden_size": width, "heads": heads,
+                                                             "qk_heads": qk_heads, "dim": dim, "vdim": vdim,
+                                                             "conv": conv, "eps": eps}))
+    g = torch.Generator().manual_seed(9)
+    qk, values = qk_heads * dim, heads * vdim
+    weights = {"q": _bf16(g, qk, width, 1.5), "k": _bf16(g, qk, width, 1.5), "v": _bf16(g, values, width, 1.5),
+               "g": _bf16(g, values, width, 1.5), "b": _bf16(g, heads, width, 1.5), "a": _bf16(g, heads, width, 1.5),
+               "o": _bf16(g, width, values),
+               "A_log": (torch.rand(heads, generator=g) * 2 - 2.5).to(torch.bfloat16),
+               "dt_bias": torch.randn(heads, generator=g).to(torch.bfloat16),
+               "norm": (1 + 0.2 * torch.randn(vdim, generator=g)).to(torch.bfloat16)}
+    for name_, rows in (("q", qk), ("k", qk), ("v", values)):
+        weights[name_ + "_conv"] = (0.6 * torch.randn(rows, conv, generator=g)).to(torch.bfloat16)
+    part.bind(weights, rt)
+    sequences = _inputs(dtype, width, 10)
+    got = _feed(PartHarness(part, dtype, 3), rt, sequences, SCHEDULE, width)
+    plain = _f64(weights)
+    for name_ in ("q", "k", "v"):
+        plain[name_ + ".conv"] = plain.pop(name_ + "_conv")
+    p = {"heads": heads, "kv_heads": qk_heads, "dim": dim, "vdim": vdim, "conv": conv}
+    for rows, h in zip(got, sequences):
+        want = P.gated_delta(plain, p, h.to(P.F64), {}, eps)
+        assert rel_error(rows, want.numpy()) <= PART_TOL[dtype]
+
+
+def _softmax_branch(width, heads, kv_heads, dim, rot_dims, base, scale):
+    from etalii.dllm_b200.parts import PartSpec
+
+    position = None if not rot_dims else PartSpec("rotary", {"head_dim": dim, "theta": base, "rotary_dim": rot_dims,
+                                                             "pairing": "interleaved"})
+    return PartSpec("attention", {"hidden_size": width, "num_heads": heads, "num_kv_heads": kv_heads,
+                                  "head_dim": dim, "scale": scale, "window": None, "position": position,
+                                  "values": "keys"})
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,rot_dims", [(6, 2, 32, 16), (4, 1, 24, 24), (2, 2, 64, 0), (4, 4, 48, 8)])
+def test_parallel_mixer_part(name, dtype, heads, kv_heads, dim, rot_dims):
+    """Softmax attention whose values are its keys, rotated on interleaved pairs, beside retention; the pieces cross
+    the cache's page border at 64."""
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    width, eps = 56, 1e-5
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "rot": {"base": 300.0, "dims": rot_dims},
+            "scale": 0.21}
+    right = {"heads": 3, "dim": 20, "vdim": 8, "decay": [0.9, 0.99, 0.75]}
+    part = build_part("mixer", PartSpec("parallel", {
+        "hidden_size": width, "eps": eps, "factor": 0.5,
+        "left": _softmax_branch(width, heads, kv_heads, dim, rot_dims, 300.0, 0.21),
+        "right": PartSpec("decay_linear_attention", {
+            "hidden_size": width, "heads": 3, "dim": 20, "vdim": 8, "decay": right["decay"], "eps": eps,
+            "key_scale": 20 ** -0.5})}))
+    g = torch.Generator().manual_seed(12)
+    weights = {"left.q": _bf16(g, heads * dim, width, 2.0), "left.k": _bf16(g, kv_heads * dim, width, 2.0),
+               "left.o": _bf16(g, width, heads * dim), "right.q": _bf16(g, 60, width, 1.5),
+               "right.k": _bf16(g, 60, width, 1.5), "right.v": _bf16(g, 24, width, 1.5),
+               "right.g": _bf16(g, 24, width, 1.5), "right.o": _bf16(g, width, 24),
+               "left.out": (1 + 0.2 * torch.randn(width, generator=g)).to(torch.bfloat16),
+               "right.out": (1 + 0.2 * torch.randn(width, generator=g)).to(torch.bfloat16)}
+    part.bind(weights, rt)
+    sequences = _inputs(dtype, width, 13)
+    got = _feed(PartHarness(part, dtype, 3), rt, sequences, SCHEDULE, width)
+    plain = P.nested({"m." + k: v for k, v in weights.items()}, "m.")
+    for rows, h in zip(got, sequences):
+        want = P.parallel_mixer(plain, {"left": left, "right": right}, h.to(P.F64), 0, {}, eps)
+        assert rel_error(rows, want.numpy()) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("name,dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 63, 64, 65, 127, 128])
+def test_one_far_key_decides_the_attention(name, dtype, far):
+    """The query matrix is the key matrix and the input at `far` is the last input times four, so that one key far
+    back (at a page's first or last row, or the sequence's first) takes nearly all the weight of the last token and
+    of the token decoded after it: a kernel that loses or misplaces that key gives another row entirely."""
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    rt = _runtime(dtype)
+    width, heads, dim = 48, 3, 32
+    part = build_part("mixer", _softmax_branch(width, heads, heads, dim, 8, 1e6, 1.0))
+    g = torch.Generator().manual_seed(20 + far)
+    shared = _bf16(g, heads * dim, width, 3.0)
+    weights = {"q": shared, "k": shared.clone(), "o": _bf16(g, width, heads * dim)}
+    part.bind(weights, rt)
+    n = 200
+    h = torch.randn(n + 1, width, generator=g).to(dtype).float()
+    h[n - 1] = h[n] = h[far] / 4
+    h = h.to(dtype).float()
+    harness = PartHarness(part, dtype, 1)
+    got = _feed(harness, rt, [h], [[(0, n)], [(0, 1)]], width)[0]
+    p = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "rot": {"base": 1e6, "dims": 8}, "scale": 1.0}
+    want = P.softmax_attention(_f64(weights), p, h.to(P.F64), 0, {}).numpy()
+    alone = (h[far:far + 1].to(P.F64) @ weights["k"].to(P.F64).T) @ weights["o"].to(P.F64).T  # the far value alone
+    for row in (n - 1, n):
+        assert rel_error(want[row], alone.numpy()[0]) < 0.2  # the test's premise: that key dominates
+        assert rel_error(got[row], want[row]) <= PART_TOL[dtype]
+
+
+# ---- whole models through the engine --------------------------------------------------------------------------------
+
+
+class Case:
+    def __init__(self, case, seed=1):
+        self.config = C.CASES[case]()
+        self.tensors = C.random_weights(self.config, seed)
+        self.plain = P.PlainTisalorn(self.config, self.tensors)
+        self._memo = {}
+
+    def logits(self, tokens):
+        key = tuple(tokens)
+        if key not in self._memo:
+            self._memo[key] = self.plain.forward(list(tokens), {})[0].numpy()
+        return self._memo[key]
+
+
+_CASES = {}
+
+
+def _case(name) -> Case:
+    if name not in _CASES:
+        _CASES[name] = Case(name)
+    return _CASES[name]
+
+
+def _run(engine, prompts, schedule, want_all=True):
+    """Feeds `prompts` by `schedule` (steps of (prompt, count)); a prompt's slot is given back with its last token.
+    Returns every position's logits per prompt."""
+    at = [0] * len(prompts)
+    slots = {}
+    rows = [[] for _ in prompts]
+    for step in schedule:
+        for i, _ in step:
+            if i not in slots:
+                slots[i] = engine.open(1)[0]
+        pieces = [prompts[i][at[i]:at[i] + n] for i, n in step]
+        out = host(engine.step([slots[i] for i, _ in step], pieces, [list(range(len(p))) for p in pieces]))
+        engine.check()
+        offset = 0
+        for (i, n) in step:
+            rows[i].append(out[offset:offset + n])
+            offset += n
+            at[i] += n
+            if at[i] == len(prompts[i]):
+                engine.close([slots.pop(i)])
+    assert not slots
+    return [np.concatenate(r) for r in rows]
+
+
+def _compare(case, got, prompts, dtype_name):
+    for rows, tokens in zip(got, prompts):
+        want = case.logits(tokens)
+        assert rows.shape == want.shape
+        assert rel_error(rows, want) <= TOL[dtype_name]
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(C.CASES))
+def test_whole_prompts_alone_and_as_one_batch(name, dtype_name):
+    case = _case(name)
+    engine = C.make_engine(case.config, case.tensors, dtype_name)
+    prompts = C.tokens_for(case.config, [1, 2, 70, 131, 5])
+    alone = _run(engine, prompts, [[(i, len(p))] for i, p in enumerate(prompts)])
+    _compare(case, alone, prompts, dtype_name)
+    together = _run(engine, prompts, [[(i, len(p)) for i, p in enumerate(prompts)]])
+    _compare(case, together, prompts, dtype_name)
+    if dtype_name == "float32":  # batch mates change nothing beyond rounding; in float32 that is very little
+        assert all(rel_error(a, b) <= 1e-5 for a, b in zip(alone, together))
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(C.CASES))
+def test_portions_and_single_tokens(name, dtype_name):
+    """One prompt cut into portions of 64, 2, 65, 3 and 1, 1, ...: the pieces cross page borders, are shorter than
+    the convolution, and end in token-by-token decoding."""
+    case = _case(name)
+    engine = C.make_engine(case.config, case.tensors, dtype_name)
+    prompt = C.tokens_for(case.config, [150], seed=6)[0]
+    schedule = [[(0, 64)], [(0, 2)], [(0, 65)], [(0, 3)]] + [[(0, 1)]] * 16
+    _compare(case, _run(engine, [prompt], schedule), [prompt], dtype_name)
+    # the first tokens one by one from an empty state, then the rest
+    schedule = [[(0, 1)]] * 5 + [[(0, 145)]]
+    _compare(case, _run(engine, [prompt], schedule), [prompt], dtype_name)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "one_round"])
+def test_unequal_batches_early_finishers_and_slots_used_again(name, dtype_name):
+    """Requests of unequal length start together and decode together; the shorter ones end earlier and give their
+    slots and pages back; later requests take those slots (state must start from zero) and run beside the survivors."""
+    case = _case(name)
+    engine = C.make_engine(case.config, case.tensors, dtype_name, max_tokens=64 * 8, max_slots=4)
+    prompts = C.tokens_for(case.config, [40, 9, 75, 30, 12], seed=8)
+    schedule = [[(0, 30), (1, 6), (2, 66)]]
+    schedule += [[(0, 1), (1, 1), (2, 1)]] * 3          # request 1 ends here
+    schedule += [[(0, 1), (2, 1)]] * 6                  # request 2 ends here
+    schedule += [[(3, 25), (4, 10)]]                    # two new requests take the freed slots
+    schedule += [[(0, 1), (3, 1), (4, 1)]]              # ... and decode beside the survivor
+    schedule += [[(3, 1), (4, 1)], [(3, 3)]]
+    got = _run(engine, prompts, schedule)
+    _compare(case, got, prompts, dtype_name)
+    engine.cache.check()
+    assert engine.cache.pages_held() == 0
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_long_decoding_through_the_decode_graph(dtype_name):
+    """A hundred single-token steps of three sequences as the generation loop runs them (one captured graph replayed),
+    then the next step's logits against the plain implementation on the whole history."""
+    case = _case("mixed")
+    engine = C.make_engine(case.config, case.tensors, dtype_name, decode_logits=True)
+    prompts = C.tokens_for(case.config, [7, 20, 66], seed=9)
+    slots = engine.open(3)
+    first = host(engine.step(slots, prompts)).argmax(axis=1).tolist()
+    chosen = engine.decode(slots, first, 100)
+    histories = [p + [f] + [step[i] for step in chosen] for i, (p, f) in enumerate(zip(prompts, first))]
+    graph_logits = host(engine.last_decode_graph.logits)  # of the last step: history without its last token
+    for i, history in enumerate(histories):
+        want = case.logits(history[:-1])[-1]
+        assert rel_error(graph_logits[i], want) <= TOL[dtype_name]
+        if dtype_name == "float32":
+            assert int(np.argmax(want)) == history[-1]
+    engine.close(slots)
+    engine.cache.check()
+
+
+def test_greedy_generation_through_the_generation_loop():
+    """`Engine.generate` (batches planned by the scheduler, prompt step, decode graphs, early finishers) gives the
+    tokens the plain implementation chooses greedily, in float32."""
+    from etalii.dllm_b200 import SamplingOptions
+
+    case = _case("plain_order")
+    engine = C.make_engine(case.config, case.tensors, "float32")
+    prompts = C.tokens_for(case.config, [3, 18, 70], seed=10)
+    results = engine.generate(prompts, 12, SamplingOptions(), ignore_eos=True)
+    for prompt, result in zip(prompts, results):
+        history = list(prompt)
+        for _ in range(12):
+            history.append(int(np.argmax(case.logits(history)[-1])))
+        assert list(result.tokens) == history[len(prompt):]
+    again = engine.generate(prompts[:2], 5, SamplingOptions(), ignore_eos=True)  # the slots are used again
+    assert [list(r.tokens) for r in again] == [list(r.tokens)[:5] for r in results[:2]]
+
+
+def test_sampled_generation_runs_in_bfloat16():
+    from etalii.dllm_b200 import SamplingOptions
+
+    case = _case("one_round")
+    engine = C.make_engine(case.config, case.tensors, "bfloat16")
+    prompts = C.tokens_for(case.config, [5, 33], seed=11)
+    a = engine.generate(prompts, 20, SamplingOptions(temperature=0.8, top_k=20, seed=3), ignore_eos=True)
+    b = engine.generate(prompts, 20, SamplingOptions(temperature=0.8, top_k=20, seed=3), ignore_eos=True)
+    assert [list(r.tokens) for r in a] == [list(r.tokens) for r in b] and all(len(r.tokens) == 20 for r in a)
+
+
+def test_trace_replay_of_a_random_model(tmp_path):
+    """bin/trace_run as a subprocess on a model folder written by the library: a prompt step, single tokens, an end."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from etalii.dllm_b200.weights.random_init import write_model
+
+    case = _case("plain_order")
+    folder = write_model(str(tmp_path / "model"), case.config, case.tensors)
+    tokens = C.tokens_for(case.config, [20], seed=12)[0]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:17], "want": [0, 16]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[17:18], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": tokens[18:20], "want": [1]}], "end": ["a"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    done = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype",
+                           "float32", "--out", str(out), "--max-tokens", "128"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                          timeout=900)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [line for line in done.stdout.split("\n") if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+    want = case.logits(tokens)
+    first = np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1)
+    last = np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1)
+    assert not (out / "1.f32").exists()
+    assert rel_error(first, want[[0, 16]]) <= TOL["float32"] and rel_error(last, want[[19]]) <= TOL["float32"]
