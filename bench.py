@@ -804,8 +804,156 @@ def reference_arm(args) -> int:
     return 0
 
 
+DESIGN_SIZES = {
+    # width, heads, kv heads, head dim (also the matrix memory's dim and vdim), feed-forward width, layers, vocabulary
+    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, ff=2816, layers=4, vocab=32000),
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=5632, layers=4, vocab=32000),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=11008, layers=3, vocab=32000),
+}
+
+
+def tisalorn_config(size: dict) -> dict:
+    """A Tisalorn model of `size`: the mixers in turn (parallel, delta, lightning, parallel, ...), no loop."""
+    h, g, d = size["heads"], size["kv_heads"], size["dim"]
+    decay = [1.0 - 2.0 ** -(5 + 4 * i / max(1, h - 1)) for i in range(h)]
+    mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    kinds = {
+        "parallel": {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "rot": {"base": 500000.0, "dims": d // 2},
+                     "scale": d ** -0.5},
+            "right": {"heads": h, "dim": d, "vdim": d, "decay": decay}}},
+        "delta": {"type": "delta", "mlp": mlp, "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "conv": 4}},
+        "lightning": {"type": "lightning", "mlp": mlp, "mixer": {"heads": h, "dim": d, "vdim": d, "decay": decay}},
+    }
+    order = ["parallel", "delta", "lightning"]
+    return {"architecture": "Tisalorn", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "max_position": 8192,
+            "layers": [kinds[order[i % 3]] for i in range(size["layers"])]}
+
+
+def llama_config_of(size: dict) -> dict:
+    return dict(SMOLLM2_135M, num_hidden_layers=size["layers"], hidden_size=size["width"],
+                num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
+                intermediate_size=size["ff"], vocab_size=size["vocab"], tie_word_embeddings=False)
+
+
+def step_trace(engine, run_step) -> dict:
+    """Every launch of one step with its device time: the stream is held busy while the host issues the step with an
+    event behind every launch, so the kernels run back to back. Returns name -> (launches, microseconds each)."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    run_step()  # (buffers, kernels)
+    torch.cuda.synchronize()
+    totals, counts = {}, {}
+    for _ in range(3):
+        torch.cuda._sleep(40_000_000)
+        ops.trace = []
+        before = torch.cuda.Event(enable_timing=True)
+        before.record()
+        run_step()
+        torch.cuda.synchronize()
+        events, ops.trace = ops.trace, None
+        for name, event in events:
+            totals[name] = totals.get(name, 0.0) + before.elapsed_time(event)
+            counts[name] = counts.get(name, 0) + 1
+            before = event
+    return {name: {"launches": counts[name] // 3, "us": round(totals[name] / counts[name] * 1e3, 2)}
+            for name in sorted(totals, key=lambda n: -totals[n])}
+
+
+def design_comparison(args) -> int:
+    """`--design tisalorn`: prefill and decode throughput of Tisalorn models at layer sizes like a real model's (random
+    weights) beside a Llama model of the same width, heads, feed-forward and depth; then where the time of a prompt
+    step and of a decode step goes, launch by launch, with the new kernels' distance to their rooflines."""
+    import gc
+
+    import numpy as np
+    import torch
+
+    from etalii.dllm_b200 import SamplingOptions
+    from etalii.dllm_b200.config.registry import config_from_dict
+    from etalii.dllm_b200.engine.decode import DecodeGraph
+    from etalii.dllm_b200.engine.engine import Engine
+
+    peak = peaks()
+    out = {"design": "Tisalorn", "beside": "llama of equal width, heads, feed-forward and depth", "dtype": "bf16",
+           "data": "synthetic: seeded random token ids, seeded random weights", "batch": args.batch,
+           "prefill_tokens": PREFILL_TOKENS, "peaks": peak["source"], "sizes": {}}
+    warmup = max(3, args.warmup)
+    steps = min(args.steps, 128)
+    for size_name in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
+        size = DESIGN_SIZES[size_name]
+        row = {"config": size}
+        for model, config_dict in (("tisalorn", tisalorn_config(size)), ("llama", llama_config_of(size))):
+            config = config_from_dict(config_dict)
+            cache_tokens = 64 * (-(-(PREFILL_TOKENS + warmup + steps + 64) // 64)) * max(args.batch, 2)
+            engine = Engine.from_random(config, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=cache_tokens,
+                                        max_length=4096)
+            vocab = size["vocab"]
+            prompts = make_prompts(args.batch, vocab, seed=1)
+            point = decode_point(engine, prompts, steps, warmup, 3)
+            measured = prefill_point(engine, vocab, warmup=3)
+            numbers = {"decode_ms_per_step": round(point["ms_per_step"], 4),
+                       "decode_tokens_per_s": round(point["tokens_per_s"], 1),
+                       "decode_launches_per_step": point["launches_per_step"],
+                       "prefill_ms": round(measured["ms"], 3), "prefill_device_ms": round(measured["device_ms"], 3),
+                       "prefill_tokens_per_s": round(PREFILL_TOKENS / (measured["ms"] / 1e3), 1)}
+            # launch by launch: one prompt step, one decode step
+            prompt = np.random.default_rng(7).integers(0, vocab, PREFILL_TOKENS).tolist()
+
+            def prompt_step():
+                slot = engine.open(1)
+                engine.step(slot, [prompt])
+                engine.close(slot)
+
+            numbers["prefill_kernels"] = step_trace(engine, prompt_step)
+            slots = engine.open(len(prompts))
+            tokens = []
+            for begin in range(0, len(prompts), 8):
+                part = slice(begin, begin + 8)
+                logits = engine.step(slots[part], prompts[part])
+                tokens += engine.sampler.choose(logits, engine.last_batch.slots, SamplingOptions()).tolist()
+            run = DecodeGraph(engine, len(prompts), SamplingOptions(), use_graph=False,
+                              max_context=max(len(p) for p in prompts) + 64)
+            engine.decode_start(run, slots, tokens, 16)
+            numbers["decode_kernels"] = step_trace(engine, lambda: run.replay(1))
+            engine.close(slots)
+            engine.check()
+            row[model] = numbers
+            del engine, run
+            gc.collect()
+            torch.cuda.empty_cache()
+        # the new kernels against their rooflines
+        h, d, b = size["heads"], size["dim"], args.batch
+        state_bytes = 2 * 4 * b * h * d * d  # a decode step reads and writes every sequence's matrices once
+        scan_fmas = {"decay_scan": 2, "delta_scan": 3}  # multiply-adds per matrix element and token
+        fp32_peak = 148 * 128 * 2 * 1.965e9  # (148 multiprocessors x 128 lanes x 2 flops at the top clock)
+        roofline = {}
+        for name, fmas in scan_fmas.items():
+            decode = row["tisalorn"]["decode_kernels"].get(name)
+            prefill = row["tisalorn"]["prefill_kernels"].get(name)
+            if decode:
+                roofline[name + "_decode_hbm_frac"] = round(state_bytes / (decode["us"] * 1e-6) / 1e9 / peak["hbm_gbs"], 4)
+            if prefill:
+                flops = 2 * fmas * PREFILL_TOKENS * h * d * d
+                roofline[name + "_prefill_fp32_frac"] = round(flops / (prefill["us"] * 1e-6) / fp32_peak, 4)
+        row["roofline"] = roofline
+        row["tisalorn_over_llama"] = {
+            "prefill": round(row["tisalorn"]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"], 3),
+            "decode": round(row["tisalorn"]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"], 3)}
+        out["sizes"][size_name] = row
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
+    parser.add_argument("--design", choices=("tisalorn",),
+                        help="instead of the benchmark: prefill and decode throughput of this design at layer sizes "
+                             "like a real model's, beside a Llama model of equal size, and its kernels' rooflines")
+    parser.add_argument("--size", default="", help="with --design: which sizes (comma separated; default all)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
@@ -837,6 +985,8 @@ def main() -> int:
         return cut_reduction_case()
     if args.profile == "sampling":
         return sampling_table()
+    if args.design:
+        return design_comparison(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2

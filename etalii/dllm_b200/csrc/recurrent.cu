@@ -9,8 +9,8 @@
 // recurrence does not involve the other columns, so columns are the parallel dimension besides heads and sequences.
 // Inside a warp a lane holds `RPL` consecutive rows of one column (8 lanes a column, 4 columns a warp): the sums over
 // rows (S^T q, S^T k) are RPL multiply-adds a lane and three shuffles. The tokens' q, k and v come through two
-// shared-memory stages filled by cp.async, so global latency is paid once per 16 tokens and hidden behind the
-// arithmetic of the stage before. Everything is float32: inputs, state, sums.
+// shared-memory stages filled by cp.async (16-byte pieces where the rows allow it), so global latency is paid once per
+// 16 tokens and hidden behind the arithmetic of the stage before. Everything is float32: inputs, state, sums.
 //
 // State layout: [slot][head][column][row], a column's rows contiguous (a lane's rows are one or more 16-byte loads).
 #include "common.cuh"
@@ -55,20 +55,26 @@ struct ScanArgs {
   const int* cu_seqlens; // sequence s has the tokens cu_seqlens[s] .. cu_seqlens[s + 1] - 1 of the step
   const int* slots;
   float* out;            // [tokens][heads * vdim]
+  int vector;            // q, k, v and their rows are 16-byte aligned and dim, vdim multiples of 4: 16-byte copies
   // decayed outer products
   const float* decay;    // [heads]
-  int activation;        // 1: q, k and v pass silu on the way in
-  float k_scale;
+  float out_scale;       // the read-out is multiplied by this (a scale of the keys, which the sums are linear in)
   // gated delta rule: per token [g (heads) | beta (heads) | k.q (qk_heads)], `aux_stride` floats a token
   const float* aux;
   int aux_stride;
 };
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
 
 // MODE 0: decayed outer products; MODE 1: gated delta rule. TOKENS: tokens a stage.
 template <int RPL, int MODE, int TOKENS>
 __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   constexpr int DIMP = RPL * 8;  // rows a stage holds per token (the head's dim rounded up)
   constexpr int PER_TOKEN = 2 * DIMP + SCAN_COLS + 4;
+  constexpr int PIECES = PER_TOKEN / 4;  // 16-byte pieces of a token's stage row
   extern __shared__ __align__(16) float stage[];  // [2][TOKENS][PER_TOKEN]: k | q | v (16 columns) | g, beta, k.q, -
   pdl_launch_dependents();
   const int head = blockIdx.y, seq = blockIdx.z, col0 = blockIdx.x * SCAN_COLS;
@@ -82,18 +88,44 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   const int slot = a.slots[seq];
   float* my_state = a.state + (((size_t)slot * a.heads + head) * a.vdim + col) * (size_t)a.dim + rg * RPL;
 
-  float S[RPL];
+  float S[RPL];  // (dim is a multiple of 4 and so is a lane's first row: a piece of 4 rows is inside the head or not)
 #pragma unroll
-  for (int j = 0; j < RPL; ++j) S[j] = (col < a.vdim && rg * RPL + j < a.dim) ? my_state[j] : 0.f;
+  for (int j = 0; j < RPL; j += 4) {
+    float4 s4 = (col < a.vdim && rg * RPL + j < a.dim) ? *reinterpret_cast<const float4*>(my_state + j)
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[j] = s4.x; S[j + 1] = s4.y; S[j + 2] = s4.z; S[j + 3] = s4.w;
+  }
 
   auto fill = [&](int chunk, int buffer) {
     float* dst = stage + (size_t)buffer * TOKENS * PER_TOKEN;
-    int t0 = chunk * TOKENS;
-    for (int i = tid; i < TOKENS * PER_TOKEN; i += SCAN_THREADS) {
-      int t = i / PER_TOKEN, e = i - t * PER_TOKEN;
-      const float* src = nullptr;
-      if (t0 + t < count) {
+    const int t0 = chunk * TOKENS, here = min(TOKENS, count - t0);
+    if (a.vector) {
+      for (int i = tid; i < here * PIECES; i += SCAN_THREADS) {
+        int t = i / PIECES, e = (i - t * PIECES) * 4;
         size_t token = (size_t)(first + t0 + t);
+        const float* src = nullptr;
+        if (e < DIMP) {
+          if (e < a.dim) src = a.k + token * a.stride + qk_head * a.dim + e;
+        } else if (e < 2 * DIMP) {
+          if (e - DIMP < a.dim) src = a.q + token * a.stride + qk_head * a.dim + (e - DIMP);
+        } else if (e < 2 * DIMP + SCAN_COLS) {
+          int c = col0 + e - 2 * DIMP;
+          if (c < a.vdim) src = a.v + token * a.stride + head * a.vdim + c;
+        } else if (MODE == 1) {
+          const float* aux = a.aux + token * a.aux_stride;
+          cp_async4(dst + t * PER_TOKEN + e, aux + head);
+          cp_async4(dst + t * PER_TOKEN + e + 1, aux + a.heads + head);
+          cp_async4(dst + t * PER_TOKEN + e + 2, aux + 2 * a.heads + qk_head);
+          continue;
+        }
+        if (src != nullptr) cp_async16(dst + t * PER_TOKEN + e, src);
+        else *reinterpret_cast<float4*>(dst + t * PER_TOKEN + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else {
+      for (int i = tid; i < here * PER_TOKEN; i += SCAN_THREADS) {
+        int t = i / PER_TOKEN, e = i - t * PER_TOKEN;
+        size_t token = (size_t)(first + t0 + t);
+        const float* src = nullptr;
         if (e < DIMP) {
           if (e < a.dim) src = a.k + token * a.stride + qk_head * a.dim + e;
         } else if (e < 2 * DIMP) {
@@ -107,27 +139,35 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
           else if (which == 1) src = a.aux + token * a.aux_stride + a.heads + head;
           else if (which == 2) src = a.aux + token * a.aux_stride + 2 * a.heads + qk_head;
         }
+        if (src != nullptr) cp_async4(dst + i, src);
+        else dst[i] = 0.f;
       }
-      if (src != nullptr) cp_async4(dst + i, src);
-      else dst[i] = 0.f;
     }
     cp_async_commit();
   };
-  // what a thread copied it also finishes (the same index walk): activation or scale in place
-  auto finish = [&](int buffer) {
-    if (MODE != 0 || (a.activation == 0 && a.k_scale == 1.0f)) return;
-    float* dst = stage + (size_t)buffer * TOKENS * PER_TOKEN;
-    for (int i = tid; i < TOKENS * PER_TOKEN; i += SCAN_THREADS) {
-      int e = i % PER_TOKEN;
-      if (e >= 2 * DIMP + SCAN_COLS) continue;
-      float value = dst[i];
-      if (a.activation == 1) value = silu_exact(value);
-      if (e < DIMP) value *= a.k_scale;
-      dst[i] = value;
+
+  // one token of the decayed sum: the state moves on, the lane's part of S^T q comes back
+  auto decayed = [&](const float* row) -> float {
+    float v = row[2 * DIMP + warp * 4 + cc];
+    float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < RPL; j += 4) {
+      float4 k4 = *reinterpret_cast<const float4*>(row + rg * RPL + j);
+      float4 q4 = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
+      S[j] = fmaf(decay, S[j], k4.x * v);
+      S[j + 1] = fmaf(decay, S[j + 1], k4.y * v);
+      S[j + 2] = fmaf(decay, S[j + 2], k4.z * v);
+      S[j + 3] = fmaf(decay, S[j + 3], k4.w * v);
+      p0 = fmaf(S[j], q4.x, p0);
+      p1 = fmaf(S[j + 1], q4.y, p1);
+      p0 = fmaf(S[j + 2], q4.z, p0);
+      p1 = fmaf(S[j + 3], q4.w, p1);
     }
+    return p0 + p1;
   };
 
   const int chunks = (count + TOKENS - 1) / TOKENS;
+  const int out_width = a.heads * a.vdim;
   if (chunks > 0) fill(0, 0);
   for (int chunk = 0; chunk < chunks; ++chunk) {
     int buffer = chunk & 1;
@@ -137,41 +177,55 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
     } else {
       cp_async_wait<0>();
     }
-    finish(buffer);
     __syncthreads();
     const float* base = stage + (size_t)buffer * TOKENS * PER_TOKEN;
-    int here = min(TOKENS, count - chunk * TOKENS);
-    for (int t = 0; t < here; ++t) {
-      const float* row = base + t * PER_TOKEN;
-      float kk[RPL], qq[RPL];
+    const int here = min(TOKENS, count - chunk * TOKENS);
+    float* out = a.out + (size_t)(first + chunk * TOKENS) * out_width + head * a.vdim + col;
+    const bool writes = rg == 0 && col < a.vdim;
+    int t = 0;
+    if (MODE == 0) {
+      // four tokens at a time: their sums over the rows are independent of one another, so the shuffles of one
+      // hide behind the arithmetic of the next
+      for (; t + 4 <= here; t += 4) {
+        float p[4];
 #pragma unroll
-      for (int j = 0; j < RPL; j += 4) {
-        float4 k4 = *reinterpret_cast<const float4*>(row + rg * RPL + j);
-        float4 q4 = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
-        kk[j] = k4.x; kk[j + 1] = k4.y; kk[j + 2] = k4.z; kk[j + 3] = k4.w;
-        qq[j] = q4.x; qq[j + 1] = q4.y; qq[j + 2] = q4.z; qq[j + 3] = q4.w;
+        for (int u = 0; u < 4; ++u) p[u] = decayed(base + (t + u) * PER_TOKEN);
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) p[u] += __shfl_xor_sync(0xffffffffu, p[u], o);
+        }
+        if (writes) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) out[(size_t)(t + u) * out_width] = p[u] * a.out_scale;
+        }
       }
-      float v = row[2 * DIMP + warp * 4 + cc];
+    }
+    for (; t < here; ++t) {
+      const float* row = base + t * PER_TOKEN;
       float o;
       if (MODE == 0) {
-        float p = 0.f;
-#pragma unroll
-        for (int j = 0; j < RPL; ++j) {
-          S[j] = fmaf(decay, S[j], kk[j] * v);
-          p = fmaf(S[j], qq[j], p);
-        }
+        float p = decayed(row);
         p += __shfl_xor_sync(0xffffffffu, p, 4);
         p += __shfl_xor_sync(0xffffffffu, p, 8);
         p += __shfl_xor_sync(0xffffffffu, p, 16);
-        o = p;
+        o = p * a.out_scale;
       } else {
+        float v = row[2 * DIMP + warp * 4 + cc];
         float g = row[2 * DIMP + SCAN_COLS], beta = row[2 * DIMP + SCAN_COLS + 1], kq = row[2 * DIMP + SCAN_COLS + 2];
-        float sk = 0.f, sq = 0.f;  // S^T k and S^T q of the state before this token
+        float kk[RPL];
+        float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f;  // S^T k and S^T q of the state before this token
 #pragma unroll
-        for (int j = 0; j < RPL; ++j) {
-          sk = fmaf(S[j], kk[j], sk);
-          sq = fmaf(S[j], qq[j], sq);
+        for (int j = 0; j < RPL; j += 4) {
+          float4 k4 = *reinterpret_cast<const float4*>(row + rg * RPL + j);
+          float4 q4 = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
+          kk[j] = k4.x; kk[j + 1] = k4.y; kk[j + 2] = k4.z; kk[j + 3] = k4.w;
+          sk0 = fmaf(S[j], k4.x, sk0); sq0 = fmaf(S[j], q4.x, sq0);
+          sk1 = fmaf(S[j + 1], k4.y, sk1); sq1 = fmaf(S[j + 1], q4.y, sq1);
+          sk0 = fmaf(S[j + 2], k4.z, sk0); sq0 = fmaf(S[j + 2], q4.z, sq0);
+          sk1 = fmaf(S[j + 3], k4.w, sk1); sq1 = fmaf(S[j + 3], q4.w, sq1);
         }
+        float sk = sk0 + sk1, sq = sq0 + sq1;
         sk += __shfl_xor_sync(0xffffffffu, sk, 4);
         sq += __shfl_xor_sync(0xffffffffu, sq, 4);
         sk += __shfl_xor_sync(0xffffffffu, sk, 8);
@@ -184,14 +238,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int j = 0; j < RPL; ++j) S[j] = fmaf(kk[j], u, g * S[j]);
       }
-      if (rg == 0 && col < a.vdim)
-        a.out[(size_t)(first + chunk * TOKENS + t) * (a.heads * a.vdim) + head * a.vdim + col] = o;
+      if (writes) out[(size_t)t * out_width] = o;
     }
     __syncthreads();  // the stage is filled again two rounds on
   }
 #pragma unroll
-  for (int j = 0; j < RPL; ++j)
-    if (col < a.vdim && rg * RPL + j < a.dim) my_state[j] = S[j];
+  for (int j = 0; j < RPL; j += 4)
+    if (col < a.vdim && rg * RPL + j < a.dim)
+      *reinterpret_cast<float4*>(my_state + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
 }
 
 template <int MODE>
@@ -215,11 +269,15 @@ static bool scan_sizes_ok(int heads, int qk_heads, int dim, int vdim, int stride
          stride > 0 && heads < 65536;
 }
 
+static int scan_vector(const float* q, const float* k, const float* v, int stride, int dim, int vdim) {
+  return (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && stride % 4 == 0 && dim % 4 == 0 && vdim % 4 == 0;
+}
+
 // Decayed outer products over the new tokens of every sequence of the step. q, k, v: pointers to the first token's
-// first head inside rows of `stride` floats (float32). activation 1 applies silu to q, k and v on the way in; keys
-// are then multiplied by k_scale. Head h decays by decay[h] per token.
+// first head inside rows of `stride` floats (float32). Head h decays by decay[h] per token. The keys count k_scale
+// times: the sums are linear in them, so the state holds the unscaled sum and the read-out is multiplied instead.
 DLLM_EXPORT int dllm_decay_scan(const float* q, const float* k, const float* v, int stride, int heads, int dim,
-                                int vdim, const float* decay, int activation, float k_scale, float* state,
+                                int vdim, const float* decay, float k_scale, float* state,
                                 const int* cu_seqlens, const int* slots, int sequences, float* out,
                                 cudaStream_t stream) {
   if (sequences <= 0) return DLLM_OK;
@@ -228,7 +286,7 @@ DLLM_EXPORT int dllm_decay_scan(const float* q, const float* k, const float* v, 
   ScanArgs a = {};
   a.q = q; a.k = k; a.v = v; a.stride = stride; a.heads = heads; a.qk_heads = heads; a.dim = dim; a.vdim = vdim;
   a.state = state; a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.decay = decay;
-  a.activation = activation; a.k_scale = k_scale;
+  a.out_scale = k_scale; a.vector = scan_vector(q, k, v, stride, dim, vdim);
   return launch_scan<0>(a, sequences, stream);
 }
 
@@ -245,7 +303,7 @@ DLLM_EXPORT int dllm_delta_scan(const float* q, const float* k, const float* v, 
   ScanArgs a = {};
   a.q = q; a.k = k; a.v = v; a.stride = stride; a.heads = heads; a.qk_heads = qk_heads; a.dim = dim; a.vdim = vdim;
   a.state = state; a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.aux = aux; a.aux_stride = aux_stride;
-  a.k_scale = 1.0f;
+  a.out_scale = 1.0f; a.vector = scan_vector(q, k, v, stride, dim, vdim);
   return launch_scan<1>(a, sequences, stream);
 }
 
@@ -270,52 +328,77 @@ struct DeltaPrepareArgs {
   int single;
 };
 
-__global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepareArgs a) {
-  extern __shared__ float values[];  // [channels]
+// A block serves one token and one unit of its channels: q/k head j (both vectors: their norms and their product), or
+// the values of head h with that head's decay and step size. A thread owns the channels it convolves.
+__device__ __forceinline__ float delta_channel(const DeltaPrepareArgs& a, const float* row, float* kept, int channels,
+                                               int local, int ch) {
+  const int history = a.n_taps - 1;
+  float x[DELTA_MAX_TAPS];
+  for (int j = 0; j < a.n_taps; ++j) {
+    int back = history - j;  // how many tokens before this one
+    x[j] = back <= local ? row[ch - (ptrdiff_t)back * a.stride]
+                         : kept[(size_t)(history - (back - local)) * channels + ch];
+  }
+  float sum = 0.f;
+  for (int j = 0; j < a.n_taps; ++j) sum = fmaf(a.taps[(size_t)ch * a.n_taps + j], x[j], sum);
+  if (a.single)  // the history moves on by this token: this thread alone reads and writes the channel
+    for (int j = 0; j < history; ++j) kept[(size_t)j * channels + ch] = x[j + 1];
+  return silu_exact(sum);
+}
+
+__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepareArgs a) {
+  __shared__ float values[2 * 256];  // q | k of one head (dim at most 256)
+  __shared__ float scale[2];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, seq = a.tok_seq[t], local = t - a.cu_seqlens[seq], slot = a.slots[seq];
+  const int t = blockIdx.x, unit = blockIdx.y;
+  const int seq = a.tok_seq[t], local = t - a.cu_seqlens[seq], slot = a.slots[seq];
   const int qk = a.qk_heads * a.dim, channels = 2 * qk + a.heads * a.vdim, history = a.n_taps - 1;
   const float* row = a.proj + (size_t)t * a.stride;
   float* kept = a.conv_state + (size_t)slot * history * channels;
-  for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
-    float x[DELTA_MAX_TAPS];
-    for (int j = 0; j < a.n_taps; ++j) {
-      int back = history - j;  // how many tokens before this one
-      x[j] = back <= local ? row[ch - (ptrdiff_t)back * a.stride] : kept[(size_t)(history - (back - local)) * channels + ch];
+  float* prepared = a.prepared + (size_t)t * channels;
+  float* aux = a.aux + (size_t)t * (2 * a.heads + a.qk_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (unit >= a.qk_heads) {  // the values of one head, and the head's decay and step size
+    const int h = unit - a.qk_heads;
+    for (int i = threadIdx.x; i < a.vdim; i += blockDim.x) {
+      int ch = 2 * qk + h * a.vdim + i;
+      prepared[ch] = delta_channel(a, row, kept, channels, local, ch);
     }
-    float sum = 0.f;
-    for (int j = 0; j < a.n_taps; ++j) sum = fmaf(a.taps[(size_t)ch * a.n_taps + j], x[j], sum);
-    values[ch] = silu_exact(sum);
-    if (a.single)  // the history moves on by this token: this thread alone reads and writes the channel
-      for (int j = 0; j < history; ++j) kept[(size_t)j * channels + ch] = x[j + 1];
+    if (threadIdx.x == 0) {
+      float z = row[a.a_off + h] + a.dt_bias[h];
+      float softplus = z > 20.f ? z : log1pf(expf(z));
+      aux[h] = expf(-expf(a.a_log[h]) * softplus);
+      aux[a.heads + h] = sigmoid_exact(row[a.b_off + h]);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < 2 * a.dim; i += blockDim.x) {
+    int ch = i < a.dim ? unit * a.dim + i : qk + unit * a.dim + (i - a.dim);
+    values[i] = delta_channel(a, row, kept, channels, local, ch);
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int vec = warp; vec < 2 * a.qk_heads; vec += warps) {  // q heads, then k heads
-    float* p = values + vec * a.dim;
+  if (warp < 2) {  // warp 0: q, warp 1: k
+    const float* p = values + warp * a.dim;
     float ss = 0.f;
     for (int i = lane; i < a.dim; i += 32) ss = fmaf(p[i], p[i], ss);
     ss = warp_sum(ss);
     float inv = 1.0f / sqrtf(ss + 1e-6f);
-    if (vec < a.qk_heads) inv *= 1.0f / sqrtf((float)a.dim);
-    for (int i = lane; i < a.dim; i += 32) p[i] *= inv;
+    if (warp == 0) inv *= 1.0f / sqrtf((float)a.dim);
+    if (lane == 0) scale[warp] = inv;
   }
   __syncthreads();
-  float* prepared = a.prepared + (size_t)t * channels;
-  for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) prepared[ch] = values[ch];
-  float* aux = a.aux + (size_t)t * (2 * a.heads + a.qk_heads);
-  for (int j = warp; j < a.qk_heads; j += warps) {
-    float dot = 0.f;
-    for (int i = lane; i < a.dim; i += 32) dot = fmaf(values[j * a.dim + i], values[qk + j * a.dim + i], dot);
-    dot = warp_sum(dot);
-    if (lane == 0) aux[2 * a.heads + j] = dot;
+  for (int i = threadIdx.x; i < 2 * a.dim; i += blockDim.x) {
+    float value = values[i] * scale[i < a.dim ? 0 : 1];
+    values[i] = value;
+    prepared[i < a.dim ? unit * a.dim + i : qk + unit * a.dim + (i - a.dim)] = value;
   }
-  for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
-    float z = row[a.a_off + h] + a.dt_bias[h];
-    float softplus = z > 20.f ? z : log1pf(expf(z));
-    aux[h] = expf(-expf(a.a_log[h]) * softplus);
-    aux[a.heads + h] = sigmoid_exact(row[a.b_off + h]);
+  __syncthreads();
+  if (warp == 0) {
+    float dot = 0.f;
+    for (int i = lane; i < a.dim; i += 32) dot = fmaf(values[i], values[a.dim + i], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) aux[2 * a.heads + unit] = dot;
   }
 }
 
@@ -347,17 +430,13 @@ DLLM_EXPORT int dllm_delta_prepare(const float* proj, int stride, int b_off, int
   if (n_taps < 1 || n_taps > DELTA_MAX_TAPS || !scan_sizes_ok(heads, qk_heads, dim, vdim, stride))
     return DLLM_UNSUPPORTED_SIZE;
   size_t channels = 2 * (size_t)qk_heads * dim + (size_t)heads * vdim;
-  if (channels * sizeof(float) > 200 * 1024) return DLLM_UNSUPPORTED_SIZE;
+  if (qk_heads + heads >= 65536) return DLLM_UNSUPPORTED_SIZE;
   if (!proj || !taps || !a_log || !dt_bias || !tok_seq || !cu_seqlens || !slots || !prepared || !aux ||
       (n_taps > 1 && !conv_state))
     return DLLM_BAD_ARGUMENT;
   DeltaPrepareArgs a = {proj, stride, b_off, a_off, taps, n_taps, a_log, dt_bias, conv_state, tok_seq, cu_seqlens,
                         slots, heads, qk_heads, dim, vdim, prepared, aux, single};
-  if (channels * sizeof(float) > 48 * 1024 &&
-      cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)(channels * sizeof(float))) != cudaSuccess)
-    return DLLM_LAUNCH_FAILED;
-  int status = dllm_launch_pdl(delta_prepare_kernel, dim3(tokens), dim3(256), channels * sizeof(float), stream, a);
+  int status = dllm_launch_pdl(delta_prepare_kernel, dim3(tokens, qk_heads + heads), dim3(128), 0, stream, a);
   if (status != DLLM_OK || single || n_taps == 1) return status;
   int across = (int)((channels + 255) / 256);
   return dllm_launch_pdl(delta_history_kernel, dim3(sequences, across), dim3(256), 0, stream, a);
@@ -368,41 +447,71 @@ DLLM_EXPORT int dllm_delta_prepare(const float* proj, int stride, int b_off, int
 // sqrt(mean square + eps), times weight[i % group] if a weight is given, times gate(z) with z the token's gate
 // pre-activations (rows of `gate_stride` floats; gate 1: silu, 2: sigmoid), rounded once to the output type.
 template <typename T>
-__global__ void __launch_bounds__(128) gated_norm_kernel(T* __restrict__ out, const float* __restrict__ x,
-                                                         const float* __restrict__ weight,
-                                                         const float* __restrict__ gate, int gate_stride, int width,
-                                                         int group, float eps, int gate_kind) {
-  __shared__ float scratch[4];
+__device__ __forceinline__ void gated_store(T* dst, const float* row, const float* weight, const float* z, int i,
+                                            int group, float inv, int gate_kind) {
+  float value = row[i] * inv;
+  if (weight != nullptr) value *= weight[i % group];
+  value *= gate_kind == 1 ? silu_exact(z[i]) : sigmoid_exact(z[i]);
+  dst[i] = from_float<T>(value);
+}
+
+// groups narrower than the row (a head's values): a warp per token and group
+template <typename T>
+__global__ void __launch_bounds__(128) gated_norm_groups_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                                const float* __restrict__ weight,
+                                                                const float* __restrict__ gate, int gate_stride,
+                                                                int tokens, int width, int group, float eps,
+                                                                int gate_kind) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = width / group, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= (long long)tokens * groups) return;
+  const int t = (int)(unit / groups), g = (int)(unit - (long long)t * groups);
   const float* row = x + (size_t)t * width;
-  const float* z = gate + (size_t)t * gate_stride;
-  T* dst = out + (size_t)t * width;
-  auto finish = [&](int i, float inv) {
-    float value = row[i] * inv;
-    if (weight != nullptr) value *= weight[i % group];
-    value *= gate_kind == 1 ? silu_exact(z[i]) : sigmoid_exact(z[i]);
-    dst[i] = from_float<T>(value);
-  };
+  float ss = 0.f;
+  for (int i = lane; i < group; i += 32) ss = fmaf(row[g * group + i], row[g * group + i], ss);
+  ss = warp_sum(ss);
+  float inv = 1.0f / sqrtf(ss / (float)group + eps);
+  for (int i = lane; i < group; i += 32)
+    gated_store<T>(out + (size_t)t * width, row, weight, gate + (size_t)t * gate_stride, g * group + i, group, inv,
+                   gate_kind);
+}
+
+// one group over the whole row: a block per token
+template <typename T>
+__global__ void __launch_bounds__(512) gated_norm_row_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                             const float* __restrict__ weight,
+                                                             const float* __restrict__ gate, int gate_stride,
+                                                             int width, float eps, int gate_kind) {
+  __shared__ float scratch[16];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const float* row = x + (size_t)t * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+  ss = warp_sum(ss);
+  if (lane == 0) scratch[warp] = ss;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < warps; ++w) total += scratch[w];
+  float inv = 1.0f / sqrtf(total / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    gated_store<T>(out + (size_t)t * width, row, weight, gate + (size_t)t * gate_stride, i, width, inv, gate_kind);
+}
+
+template <typename T>
+static int launch_gated_norm(T* out, const float* x, const float* weight, const float* gate, int gate_stride,
+                             int tokens, int width, int group, float eps, int gate_kind, cudaStream_t stream) {
   if (group == width) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
-    ss = warp_sum(ss);
-    if (lane == 0) scratch[warp] = ss;
-    __syncthreads();
-    float total = scratch[0] + scratch[1] + scratch[2] + scratch[3];
-    float inv = 1.0f / sqrtf(total / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) finish(i, inv);
-    return;
+    int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    return dllm_launch_pdl(gated_norm_row_kernel<T>, dim3(tokens), dim3(threads), 0, stream, out, x, weight, gate,
+                           gate_stride, width, eps, gate_kind);
   }
-  for (int g = warp; g < width / group; g += 4) {
-    float ss = 0.f;
-    for (int i = lane; i < group; i += 32) ss = fmaf(row[g * group + i], row[g * group + i], ss);
-    ss = warp_sum(ss);
-    float inv = 1.0f / sqrtf(ss / (float)group + eps);
-    for (int i = lane; i < group; i += 32) finish(g * group + i, inv);
-  }
+  long long units = (long long)tokens * (width / group);
+  return dllm_launch_pdl(gated_norm_groups_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, out, x,
+                         weight, gate, gate_stride, tokens, width, group, eps, gate_kind);
 }
 
 DLLM_EXPORT int dllm_gated_norm(void* out, const float* x, const float* weight, const float* gate, int gate_stride,
@@ -412,10 +521,29 @@ DLLM_EXPORT int dllm_gated_norm(void* out, const float* x, const float* weight, 
   if (width <= 0 || group <= 0 || width % group || (gate_kind != 1 && gate_kind != 2)) return DLLM_UNSUPPORTED_SIZE;
   if (!out || !x || !gate) return DLLM_BAD_ARGUMENT;
   if (out_dtype == DLLM_F32)
-    return dllm_launch_pdl(gated_norm_kernel<float>, dim3(tokens), dim3(128), 0, stream, (float*)out, x, weight, gate,
-                           gate_stride, width, group, eps, gate_kind);
+    return launch_gated_norm((float*)out, x, weight, gate, gate_stride, tokens, width, group, eps, gate_kind, stream);
   if (out_dtype == DLLM_BF16)
-    return dllm_launch_pdl(gated_norm_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, (__nv_bfloat16*)out,
-                           x, weight, gate, gate_stride, width, group, eps, gate_kind);
+    return launch_gated_norm((__nv_bfloat16*)out, x, weight, gate, gate_stride, tokens, width, group, eps, gate_kind,
+                             stream);
   return DLLM_BAD_ARGUMENT;
+}
+
+// ---- silu in place on the first `columns` values of every row (q, k and v of a mixer whose inputs are activated) ---
+__global__ void silu_columns_kernel(float* __restrict__ rows, long long total, int columns, int stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i / columns;
+    float* at = rows + r * stride + (i - r * columns);
+    *at = silu_exact(*at);
+  }
+}
+
+DLLM_EXPORT int dllm_silu_columns(float* rows, int n_rows, int columns, int stride, cudaStream_t stream) {
+  if (n_rows <= 0 || columns <= 0) return DLLM_OK;
+  if (rows == nullptr || stride < columns) return DLLM_BAD_ARGUMENT;
+  long long total = (long long)n_rows * columns;
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  return dllm_launch_pdl(silu_columns_kernel, dim3(blocks), dim3(256), 0, stream, rows, total, columns, stride);
 }

@@ -30,8 +30,9 @@ _prototypes = {
     ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                                 c_float, c_void_p],
     ("elementwise", "dllm_concat_restart"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    ("recurrent", "dllm_decay_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+    ("recurrent", "dllm_decay_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    ("recurrent", "dllm_silu_columns"): [c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "dllm_delta_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     ("recurrent", "dllm_delta_prepare"): [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -260,16 +261,21 @@ def decay_scan(out: torch.Tensor, rows: torch.Tensor, q_at: int, k_at: int, v_at
                decay: torch.Tensor, silu_inputs: bool, k_scale: float, state: torch.Tensor, batch) -> None:
     """Per sequence and head, over the step's tokens in order: S <- decay_h S + k v^T, out = S^T q, from and to
     `state` [slots, heads, vdim, dim] (float32, S stored column by column). `rows` [tokens, n] float32 holds q, k
-    and v of a token at the column offsets q_at, k_at, v_at; with `silu_inputs` they pass silu first; k is multiplied
-    by k_scale."""
+    and v of a token at the column offsets q_at, k_at, v_at; with `silu_inputs` the columns from q_at to the end of v
+    (which must lie one behind the other) pass silu first, in place; k counts k_scale times (the sums are linear in
+    k: the state holds the unscaled sum and the read-out is multiplied)."""
     _cuda(out, rows, decay, state)
     assert rows.dtype == torch.float32 and out.dtype == torch.float32 and state.dtype == torch.float32
     assert decay.dtype == torch.float32 and decay.numel() == heads
     assert tuple(state.shape[1:]) == (heads, vdim, dim) and out.shape[1] == heads * vdim
     assert rows.shape[0] >= batch.n_tokens and out.shape[0] >= batch.n_tokens
+    if silu_inputs:
+        assert q_at == 0 and k_at == heads * dim and v_at == 2 * heads * dim
+        _check(_fn("recurrent", "dllm_silu_columns")(rows.data_ptr(), batch.n_tokens, v_at + heads * vdim,
+                                                     rows.shape[1], _stream()), "silu_columns")
     _check(_fn("recurrent", "dllm_decay_scan")(
         _columns(rows, q_at), _columns(rows, k_at), _columns(rows, v_at), rows.shape[1], heads, dim, vdim,
-        decay.data_ptr(), 1 if silu_inputs else 0, float(k_scale), state.data_ptr(), batch.cu_seqlens.data_ptr(),
+        decay.data_ptr(), float(k_scale), state.data_ptr(), batch.cu_seqlens.data_ptr(),
         batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(), _stream()), "decay_scan",
         lambda: f"dim={dim} (a multiple of 4, at most 256)")
 

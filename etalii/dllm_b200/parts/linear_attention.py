@@ -128,8 +128,6 @@ class GatedDeltaRule:
             return f"dim {self.dim}: the scan keeps a head's rows in 16-byte pieces, a multiple of 4 up to 256"
         if not 1 <= self.conv <= 8:
             return f"a convolution of {self.conv} taps: the kernel takes 1 to 8"
-        if self.channels * 4 > 200 * 1024:
-            return f"{self.channels} convolved channels: a token's channels must fit a block's shared memory (51,200)"
         return row_rule(rt, hidden_size=self.hidden_size, **{"heads x vdim": self.heads * self.vdim})
 
     def cache_need(self) -> CacheNeed:
