@@ -893,6 +893,14 @@ def design_comparison(args) -> int:
                                         max_length=4096)
             vocab = size["vocab"]
             prompts = make_prompts(args.batch, vocab, seed=1)
+            if args.profile in ("prefill", "decode"):  # a small case for ncu: a few steps, no JSON
+                if model == "tisalorn" and args.profile == "prefill":
+                    print(f"profile prefill ({size_name}): {prefill_run(engine, vocab, warmup=1, repeats=1):.4f} ms")
+                elif model == "tisalorn":
+                    ms, launches, _ = decode_run(engine, prompts, 8, 3)
+                    print(f"profile decode ({size_name}): {ms / 8:.4f} ms per step, {launches} launches per step")
+                del engine
+                continue
             point = decode_point(engine, prompts, steps, warmup, 3)
             measured = prefill_point(engine, vocab, warmup=3)
             numbers = {"decode_ms_per_step": round(point["ms_per_step"], 4),
@@ -925,6 +933,8 @@ def design_comparison(args) -> int:
             del engine, run
             gc.collect()
             torch.cuda.empty_cache()
+        if args.profile in ("prefill", "decode"):
+            continue
         # the new kernels against their rooflines
         h, d, b = size["heads"], size["dim"], args.batch
         state_bytes = 2 * 4 * b * h * d * d  # a decode step reads and writes every sequence's matrices once
@@ -944,7 +954,8 @@ def design_comparison(args) -> int:
             "prefill": round(row["tisalorn"]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"], 3),
             "decode": round(row["tisalorn"]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"], 3)}
         out["sizes"][size_name] = row
-    print(json.dumps(out))
+    if args.profile not in ("prefill", "decode"):
+        print(json.dumps(out))
     return 0
 
 

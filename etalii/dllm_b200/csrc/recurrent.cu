@@ -7,17 +7,15 @@
 // One kernel serves prompts and single tokens: a block owns 16 columns of one head's S for one sequence and walks
 // that sequence's new tokens in order, from the state the cache holds to the state it leaves there. A column's
 // recurrence does not involve the other columns, so columns are the parallel dimension besides heads and sequences.
-// Inside a warp a lane holds `RPL` consecutive rows of one column (8 lanes a column, 4 columns a warp): the sums over
-// rows (S^T q, S^T k) are RPL multiply-adds a lane and three shuffles. The tokens' q, k and v come through two
+// Inside a warp a lane holds `RPL` consecutive rows of one column (8, 16 or 32 lanes a column): the sums over
+// rows (S^T q, S^T k) are RPL multiply-adds a lane and three to five shuffles. The tokens' q, k and v come through two
 // shared-memory stages filled by cp.async (16-byte pieces where the rows allow it), so global latency is paid once per
 // 16 tokens and hidden behind the arithmetic of the stage before. Everything is float32: inputs, state, sums.
 //
 // State layout: [slot][head][column][row], a column's rows contiguous (a lane's rows are one or more 16-byte loads).
 #include "common.cuh"
 
-#define SCAN_WARPS 4
-#define SCAN_COLS (4 * SCAN_WARPS)
-#define SCAN_THREADS (32 * SCAN_WARPS)
+#define SCAN_COLS 16  // columns of S a block owns
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -69,10 +67,15 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
 
-// MODE 0: decayed outer products; MODE 1: gated delta rule. TOKENS: tokens a stage.
-template <int RPL, int MODE, int TOKENS>
-__global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
-  constexpr int DIMP = RPL * 8;  // rows a stage holds per token (the head's dim rounded up)
+// MODE 0: decayed outer products; MODE 1: gated delta rule. TOKENS: tokens a stage. LPC lanes share a column (8, 16
+// or 32), each with RPL rows of it: the block has 16 * LPC threads. Few lanes a column mean few shuffles and few
+// instructions a token; many lanes mean more warps to hide latency behind, which is what a step with few sequences
+// and heads needs (one warp per scheduler issues a dependent instruction every four cycles and no faster).
+template <int RPL, int LPC, int MODE, int TOKENS>
+__global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
+  constexpr int DIMP = RPL * LPC;  // rows a stage holds per token (the head's dim rounded up)
+  constexpr int CPW = 32 / LPC;    // columns a warp owns
+  constexpr int SCAN_THREADS = SCAN_COLS * LPC;
   constexpr int PER_TOKEN = 2 * DIMP + SCAN_COLS + 4;
   constexpr int PIECES = PER_TOKEN / 4;  // 16-byte pieces of a token's stage row
   extern __shared__ __align__(16) float stage[];  // [2][TOKENS][PER_TOKEN]: k | q | v (16 columns) | g, beta, k.q, -
@@ -80,8 +83,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
   const int head = blockIdx.y, seq = blockIdx.z, col0 = blockIdx.x * SCAN_COLS;
   const int qk_head = head / (a.heads / a.qk_heads);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rg = lane >> 2, cc = lane & 3;
-  const int col = col0 + warp * 4 + cc;
+  const int rg = lane / CPW, cc = lane % CPW;
+  const int col = col0 + warp * CPW + cc;
   const float decay = MODE == 0 ? a.decay[head] : 0.f;
   pdl_wait();
   const int first = a.cu_seqlens[seq], count = a.cu_seqlens[seq + 1] - first;
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
 
   // one token of the decayed sum: the state moves on, the lane's part of S^T q comes back
   auto decayed = [&](const float* row) -> float {
-    float v = row[2 * DIMP + warp * 4 + cc];
+    float v = row[2 * DIMP + warp * CPW + cc];
     float p0 = 0.f, p1 = 0.f;
 #pragma unroll
     for (int j = 0; j < RPL; j += 4) {
@@ -191,7 +194,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) p[u] = decayed(base + (t + u) * PER_TOKEN);
 #pragma unroll
-        for (int o = 4; o <= 16; o <<= 1) {
+        for (int o = CPW; o <= 16; o <<= 1) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) p[u] += __shfl_xor_sync(0xffffffffu, p[u], o);
         }
@@ -206,12 +209,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
       float o;
       if (MODE == 0) {
         float p = decayed(row);
-        p += __shfl_xor_sync(0xffffffffu, p, 4);
-        p += __shfl_xor_sync(0xffffffffu, p, 8);
-        p += __shfl_xor_sync(0xffffffffu, p, 16);
+#pragma unroll
+        for (int o2 = CPW; o2 <= 16; o2 <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o2);
         o = p * a.out_scale;
       } else {
-        float v = row[2 * DIMP + warp * 4 + cc];
+        float v = row[2 * DIMP + warp * CPW + cc];
         float g = row[2 * DIMP + SCAN_COLS], beta = row[2 * DIMP + SCAN_COLS + 1], kq = row[2 * DIMP + SCAN_COLS + 2];
         float kk[RPL];
         float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f;  // S^T k and S^T q of the state before this token
@@ -226,12 +228,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
           sk1 = fmaf(S[j + 3], k4.w, sk1); sq1 = fmaf(S[j + 3], q4.w, sq1);
         }
         float sk = sk0 + sk1, sq = sq0 + sq1;
-        sk += __shfl_xor_sync(0xffffffffu, sk, 4);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-        sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-        sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+#pragma unroll
+        for (int o2 = CPW; o2 <= 16; o2 <<= 1) {
+          sk += __shfl_xor_sync(0xffffffffu, sk, o2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, o2);
+        }
         // (g S + k u^T)^T q = g S^T q + u (k . q): the read-out of the state after the write, without a second sum
         float u = beta * (v - g * sk);
         o = fmaf(g, sq, u * kq);
@@ -251,17 +252,23 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_kernel(ScanArgs a) {
 template <int MODE>
 static int launch_scan(const ScanArgs& a, int sequences, cudaStream_t stream) {
   dim3 grid((a.vdim + SCAN_COLS - 1) / SCAN_COLS, a.heads, sequences);
-  int rows_per_lane = (a.dim + 7) / 8;
-#define SCAN_CASE(RPL, TOKENS)                                                                                    \
-  {                                                                                                               \
-    size_t bytes = 2 * (size_t)TOKENS * (2 * RPL * 8 + SCAN_COLS + 4) * sizeof(float);                            \
-    return dllm_launch_pdl(scan_kernel<RPL, MODE, TOKENS>, grid, dim3(SCAN_THREADS), bytes, stream, a);           \
+  // rows a lane: the head's dim over the lanes of a column, in whole 16-byte pieces; the fewest lanes a column that
+  // still put about twelve warps on every multiprocessor (or the most that the dim allows)
+  long long blocks = (long long)grid.x * grid.y * grid.z;
+  int dimp = a.dim <= 32 ? 32 : (a.dim <= 64 ? 64 : (a.dim <= 128 ? 128 : 256));
+  int lanes = 8;
+  while (lanes < 32 && dimp / (2 * lanes) >= 4 && blocks * (lanes / 2) < 148 * 12) lanes *= 2;
+#define SCAN_CASE(RPL, LPC, TOKENS)                                                                               \
+  if (dimp == RPL * LPC && lanes == LPC) {                                                                        \
+    size_t bytes = 2 * (size_t)TOKENS * (2 * RPL * LPC + SCAN_COLS + 4) * sizeof(float);                          \
+    return dllm_launch_pdl(scan_kernel<RPL, LPC, MODE, TOKENS>, grid, dim3(SCAN_COLS * LPC), bytes, stream, a);   \
   }
-  if (rows_per_lane <= 4) SCAN_CASE(4, 16)
-  if (rows_per_lane <= 8) SCAN_CASE(8, 16)
-  if (rows_per_lane <= 16) SCAN_CASE(16, 16)
-  SCAN_CASE(32, 8)
+  SCAN_CASE(4, 8, 16)
+  SCAN_CASE(8, 8, 16) SCAN_CASE(4, 16, 16)
+  SCAN_CASE(16, 8, 16) SCAN_CASE(8, 16, 16) SCAN_CASE(4, 32, 16)
+  SCAN_CASE(32, 8, 8) SCAN_CASE(16, 16, 8) SCAN_CASE(8, 32, 8)
 #undef SCAN_CASE
+  return DLLM_UNSUPPORTED_SIZE;
 }
 
 static bool scan_sizes_ok(int heads, int qk_heads, int dim, int vdim, int stride) {

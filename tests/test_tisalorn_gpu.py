@@ -40,7 +40,7 @@ class PartHarness:
 
         need = part.cache_need()
         flat = list(need.parts) if need.kind == "several" else [need]
-        self.cache = PagedCache(flat, 64 * 24, 512, dtype=dtype, device=DEV)
+        self.cache = PagedCache(flat, 64 * max(24, sequences), 512, dtype=dtype, device=DEV)
         views = [self.cache.kv_view(i) if n.kind == "kv" else self.cache.state(i) for i, n in enumerate(flat)]
         self.view = tuple(views) if need.kind == "several" else views[0]
         self.part, self.buffers = part, BatchBuffers(DEV)
@@ -225,6 +225,54 @@ def test_gated_delta_rule_part(name, dtype, heads, qk_heads, dim, vdim, conv):
     p = {"heads": heads, "kv_heads": qk_heads, "dim": dim, "vdim": vdim, "conv": conv}
     for rows, h in zip(got, sequences):
         want = P.gated_delta(plain, p, h.to(P.F64), {}, eps)
+        assert rel_error(rows, want.numpy()) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("kind", ["decay", "delta"])
+def test_many_sequences_take_the_scan_with_few_lanes_a_column(kind):
+    """Sixty short sequences with eight heads: enough blocks that the scan keeps a column on eight lanes (the layout
+    for full devices), where the tests above, with three sequences, spread a column over more."""
+    from etalii.dllm_b200.parts import PartSpec, build_part
+
+    dtype = torch.float32
+    rt = _runtime(dtype)
+    width, eps, heads, dim, vdim = 40, 1e-5, 8, 64, 64
+    g = torch.Generator().manual_seed(31)
+    weights = {"q": _bf16(g, heads * dim, width, 1.5), "k": _bf16(g, heads * dim, width, 1.5),
+               "v": _bf16(g, heads * vdim, width, 1.5), "g": _bf16(g, heads * vdim, width, 1.5),
+               "o": _bf16(g, width, heads * vdim)}
+    decay = [0.5 + 0.06 * i for i in range(heads)]
+    if kind == "decay":
+        part = build_part("mixer", PartSpec("decay_linear_attention", {
+            "hidden_size": width, "heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "eps": eps,
+            "key_scale": 0.125}))
+    else:
+        part = build_part("mixer", PartSpec("gated_delta_rule", {"hidden_size": width, "heads": heads, "qk_heads": 4,
+                                                                 "dim": dim, "vdim": vdim, "conv": 2, "eps": eps}))
+        weights.update({"q": _bf16(g, 4 * dim, width, 1.5), "k": _bf16(g, 4 * dim, width, 1.5),
+                        "b": _bf16(g, heads, width, 1.5), "a": _bf16(g, heads, width, 1.5),
+                        "A_log": (torch.rand(heads, generator=g) - 1.5).to(torch.bfloat16),
+                        "dt_bias": torch.randn(heads, generator=g).to(torch.bfloat16),
+                        "norm": (1 + 0.2 * torch.randn(vdim, generator=g)).to(torch.bfloat16),
+                        "q_conv": (0.6 * torch.randn(4 * dim, 2, generator=g)).to(torch.bfloat16),
+                        "k_conv": (0.6 * torch.randn(4 * dim, 2, generator=g)).to(torch.bfloat16),
+                        "v_conv": (0.6 * torch.randn(heads * vdim, 2, generator=g)).to(torch.bfloat16)})
+    part.bind(weights, rt)
+    lengths = [2 + i % 5 for i in range(60)]
+    sequences = [torch.randn(n, width, generator=g) for n in lengths]
+    schedule = [[(i, n - 1) for i, n in enumerate(lengths)], [(i, 1) for i in range(60)]]
+    got = _feed(PartHarness(part, dtype, 60), rt, sequences, schedule, width)
+    plain = _f64(weights)
+    for name_ in ("q", "k", "v"):
+        if name_ + "_conv" in plain:
+            plain[name_ + ".conv"] = plain.pop(name_ + "_conv")
+    for rows, h in zip(got, sequences):
+        if kind == "decay":
+            want = P.retention(plain, {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}, h.to(P.F64),
+                               torch.zeros(heads, dim, vdim, dtype=P.F64), eps)
+        else:
+            want = P.gated_delta(plain, {"heads": heads, "kv_heads": 4, "dim": dim, "vdim": vdim, "conv": 2},
+                                 h.to(P.F64), {}, eps)
         assert rel_error(rows, want.numpy()) <= PART_TOL[dtype]
 
 
