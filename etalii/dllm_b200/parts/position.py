@@ -55,6 +55,12 @@ class RotaryEmbedding:
         self.rotary_dim = int(rotary_dim) if rotary_dim else self.head_dim
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
+        self.rotated = self.rotary_dim
+        """Dimensions of a head that turn. For interleaved pairs of an even head, the kernels are told that the
+        whole head turns (`rotary_dim` = head_dim, which is what the products that end in the rotation take): the
+        pairs beyond `rotated` get the angle zero, whose cosine and sine are exactly 1 and 0."""
+        if pairing == "interleaved" and self.head_dim % 2 == 0:
+            self.rotary_dim = self.head_dim
         self.theta = float(theta)
         self.scaling = dict(scaling) if scaling else None
         self._table = None
@@ -64,10 +70,13 @@ class RotaryEmbedding:
         return {}
 
     def bind(self, tensors, rt) -> None:
-        key = ("rotary", self.rotary_dim, self.theta, tuple(sorted((self.scaling or {}).items())), rt.max_length)
+        key = ("rotary", self.rotary_dim, self.rotated, self.theta, tuple(sorted((self.scaling or {}).items())),
+               rt.max_length)
 
         def make() -> torch.Tensor:
-            freqs = torch.tensor(rotary_frequencies(self.rotary_dim, self.theta, self.scaling), dtype=torch.float64)
+            values = rotary_frequencies(self.rotated, self.theta, self.scaling)
+            values += [0.0] * ((self.rotary_dim - self.rotated) // 2)  # (pairs that stay as they are)
+            freqs = torch.tensor(values, dtype=torch.float64)
             angles = torch.arange(rt.max_length, dtype=torch.float64)[:, None] * freqs[None, :]
             table = torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).to(torch.float32)
             return table.contiguous().to(rt.device)
@@ -80,12 +89,17 @@ class RotaryEmbedding:
     def row_order(self) -> list[int] | None:
         """For each place of a head as the kernels see it, the dimension of the model's head that belongs there (None:
         they are the same). Pair i of an interleaved head, dimensions (2i, 2i + 1), goes to the places
-        (i, i + rotary_dim / 2); dimensions beyond rotary_dim stay."""
+        (i, i + rotary_dim / 2)."""
         if self.pairing == "halves":
             return None
-        half = self.rotary_dim // 2
-        return [2 * i for i in range(half)] + [2 * i + 1 for i in range(half)] + \
-            list(range(self.rotary_dim, self.head_dim))
+        half = self.rotated // 2
+        rest = list(range(self.rotated, self.head_dim))
+        if self.rotary_dim == self.rotated:  # (an odd head: the rest lies behind the rotated places)
+            return [2 * i for i in range(half)] + [2 * i + 1 for i in range(half)] + rest
+        # the whole head is a rotation of halves: the dimensions that do not turn fill both halves up, as pairs
+        # with the angle zero
+        return [2 * i for i in range(half)] + rest[:len(rest) // 2] + \
+            [2 * i + 1 for i in range(half)] + rest[len(rest) // 2:]
 
 
 register_part("position", "rotary", RotaryEmbedding)
