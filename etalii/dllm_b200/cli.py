@@ -23,7 +23,7 @@ def _ids(text: str) -> list[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    parser = argparse.ArgumentParser(prog="dllm-b200", description="Llama generation on one B200")
+    parser = argparse.ArgumentParser(prog="dllm-b200", description="generation on one B200 (Llama, Tisalorn)")
     parser.add_argument("--model", help="folder with config.json and model.safetensors")
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
