@@ -92,6 +92,8 @@ def build_spec(config: TisalornConfig) -> ModelSpec:
         final_norm=PartSpec("layernorm", {"hidden_size": width, "eps": eps}, {"weight": "final.norm"}),
         head=PartSpec("linear", {"vocab_size": config.vocab, "hidden_size": width}, {"weight": "head"}),
         schedule=tuple(schedule), reentries=reentries, stop_token_ids=tuple(config.eos_token_ids),
+        # (a layer without a feed-forward has no use for a second norm; a checkpoint that stores one all the same loads)
+        ignored_suffixes=tuple(f"l{i}.norm2" for i, layer in enumerate(config.layers) if layer.get("mlp") is None),
     )
 
 

@@ -322,7 +322,7 @@ DLLM_EXPORT int dllm_delta_scan(const float* q, const float* k, const float* v, 
 // sqrt(sum of squares + 1e-6) per head, q also multiplied by dim^(-1/2). Written: prepared[t][channels] and
 // aux[t] = [g (heads) | beta (heads) | k.q (qk_heads)] with beta = sigmoid(b), g = exp(-exp(A_log) softplus(a +
 // dt_bias)). In a step of single tokens (`single` != 0) the block also moves the convolution's history on.
-#define DELTA_MAX_TAPS 8
+#define DELTA_MAX_TAPS 16
 
 struct DeltaPrepareArgs {
   const float* proj; int stride; int b_off, a_off;

@@ -299,7 +299,7 @@ def delta_prepare(prepared: torch.Tensor, aux: torch.Tensor, rows: torch.Tensor,
         dt_bias.data_ptr(), history.data_ptr() if history is not None else None, batch.tok_seq.data_ptr(),
         batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), batch.n_tokens, batch.n_seqs, heads, qk_heads, dim, vdim,
         prepared.data_ptr(), aux.data_ptr(), 1 if batch.is_decode else 0, _stream()), "delta_prepare",
-        lambda: f"taps={width} (at most 8), dim={dim} (a multiple of 4, at most 256)")
+        lambda: f"taps={width} (at most 16), dim={dim} (a multiple of 4, at most 256)")
     if not batch.is_decode and width > 1:
         global launches
         launches += 1  # (the history's own small kernel)

@@ -126,8 +126,8 @@ class GatedDeltaRule:
     def supports(self, rt) -> str | None:
         if self.dim % 4 or self.dim > 256:
             return f"dim {self.dim}: the scan keeps a head's rows in 16-byte pieces, a multiple of 4 up to 256"
-        if not 1 <= self.conv <= 8:
-            return f"a convolution of {self.conv} taps: the kernel takes 1 to 8"
+        if not 1 <= self.conv <= 16:
+            return f"a convolution of {self.conv} taps: the kernel takes 1 to 16"
         return row_rule(rt, hidden_size=self.hidden_size, **{"heads x vdim": self.heads * self.vdim})
 
     def cache_need(self) -> CacheNeed:
