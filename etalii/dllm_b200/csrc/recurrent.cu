@@ -71,14 +71,14 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 // 16), each with RPL rows of it: the block has 16 * LPC threads. Few lanes a column mean few shuffles and few
 // instructions a token; many lanes mean more warps to hide latency behind, which is what a step with few sequences
 // and heads needs (one warp per scheduler issues a dependent instruction every four cycles and no faster).
-template <int RPL, int LPC, int MODE, int TOKENS>
+template <int RPL, int LPC, int MODE, int TOKENS, int STAGES>
 __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
   constexpr int DIMP = RPL * LPC;  // rows a stage holds per token (the head's dim rounded up)
   constexpr int CPW = 32 / LPC;    // columns a warp owns
   constexpr int SCAN_THREADS = SCAN_COLS * LPC;
   constexpr int PER_TOKEN = 2 * DIMP + SCAN_COLS + 4;
   constexpr int PIECES = PER_TOKEN / 4;  // 16-byte pieces of a token's stage row
-  extern __shared__ __align__(16) float stage[];  // [2][TOKENS][PER_TOKEN]: k | q | v (16 columns) | g, beta, k.q, -
+  extern __shared__ __align__(16) float stage[];  // [STAGES][TOKENS][PER_TOKEN]: k | q | v (16 columns) | g, beta, k.q, -
   pdl_launch_dependents();
   const int head = blockIdx.y, seq = blockIdx.z, col0 = blockIdx.x * SCAN_COLS;
   const int qk_head = head / (a.heads / a.qk_heads);
@@ -103,26 +103,31 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
     float* dst = stage + (size_t)buffer * TOKENS * PER_TOKEN;
     const int t0 = chunk * TOKENS, here = min(TOKENS, count - t0);
     if (a.vector) {
+      // (the chunk's first rows once, 32-bit offsets from there: the copies are most of what a token costs besides
+      // its arithmetic)
+      const float* k0 = a.k + (size_t)(first + t0) * a.stride + qk_head * a.dim;
+      const float* q0 = a.q + (size_t)(first + t0) * a.stride + qk_head * a.dim;
+      const float* v0 = a.v + (size_t)(first + t0) * a.stride + head * a.vdim + col0;
       for (int i = tid; i < here * PIECES; i += SCAN_THREADS) {
         int t = i / PIECES, e = (i - t * PIECES) * 4;
-        size_t token = (size_t)(first + t0 + t);
+        float* to = dst + t * PER_TOKEN + e;
+        int row = t * a.stride;
         const float* src = nullptr;
         if (e < DIMP) {
-          if (e < a.dim) src = a.k + token * a.stride + qk_head * a.dim + e;
+          if (e < a.dim) src = k0 + row + e;
         } else if (e < 2 * DIMP) {
-          if (e - DIMP < a.dim) src = a.q + token * a.stride + qk_head * a.dim + (e - DIMP);
+          if (e - DIMP < a.dim) src = q0 + row + (e - DIMP);
         } else if (e < 2 * DIMP + SCAN_COLS) {
-          int c = col0 + e - 2 * DIMP;
-          if (c < a.vdim) src = a.v + token * a.stride + head * a.vdim + c;
+          if (col0 + e - 2 * DIMP < a.vdim) src = v0 + row + (e - 2 * DIMP);
         } else if (MODE == 1) {
-          const float* aux = a.aux + token * a.aux_stride;
-          cp_async4(dst + t * PER_TOKEN + e, aux + head);
-          cp_async4(dst + t * PER_TOKEN + e + 1, aux + a.heads + head);
-          cp_async4(dst + t * PER_TOKEN + e + 2, aux + 2 * a.heads + qk_head);
+          const float* aux = a.aux + (size_t)(first + t0 + t) * a.aux_stride;
+          cp_async4(to, aux + head);
+          cp_async4(to + 1, aux + a.heads + head);
+          cp_async4(to + 2, aux + 2 * a.heads + qk_head);
           continue;
         }
-        if (src != nullptr) cp_async16(dst + t * PER_TOKEN + e, src);
-        else *reinterpret_cast<float4*>(dst + t * PER_TOKEN + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src != nullptr) cp_async16(to, src);
+        else *reinterpret_cast<float4*>(to) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     } else {
       for (int i = tid; i < here * PER_TOKEN; i += SCAN_THREADS) {
@@ -149,37 +154,38 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
     cp_async_commit();
   };
 
-  // one token of the decayed sum: the state moves on, the lane's part of S^T q comes back
+  // one token of the decayed sum: the state moves on, the lane's part of S^T q comes back. Two rows an instruction
+  // (the packed float32 multiply-add of sm_100: the same roundings as two single ones, half the issue slots).
   auto decayed = [&](const float* row) -> float {
     float v = row[2 * DIMP + warp * CPW + cc];
-    float p0 = 0.f, p1 = 0.f;
+    const float2 vv = make_float2(v, v), dd = make_float2(decay, decay);
+    float2 p = make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < RPL; j += 4) {
       float4 k4 = *reinterpret_cast<const float4*>(row + rg * RPL + j);
       float4 q4 = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
-      S[j] = fmaf(decay, S[j], k4.x * v);
-      S[j + 1] = fmaf(decay, S[j + 1], k4.y * v);
-      S[j + 2] = fmaf(decay, S[j + 2], k4.z * v);
-      S[j + 3] = fmaf(decay, S[j + 3], k4.w * v);
-      p0 = fmaf(S[j], q4.x, p0);
-      p1 = fmaf(S[j + 1], q4.y, p1);
-      p0 = fmaf(S[j + 2], q4.z, p0);
-      p1 = fmaf(S[j + 3], q4.w, p1);
+      float2 s01 = __ffma2_rn(dd, make_float2(S[j], S[j + 1]), __fmul2_rn(make_float2(k4.x, k4.y), vv));
+      float2 s23 = __ffma2_rn(dd, make_float2(S[j + 2], S[j + 3]), __fmul2_rn(make_float2(k4.z, k4.w), vv));
+      S[j] = s01.x; S[j + 1] = s01.y; S[j + 2] = s23.x; S[j + 3] = s23.y;
+      p = __ffma2_rn(s01, make_float2(q4.x, q4.y), p);
+      p = __ffma2_rn(s23, make_float2(q4.z, q4.w), p);
     }
-    return p0 + p1;
+    return p.x + p.y;
   };
 
   const int chunks = (count + TOKENS - 1) / TOKENS;
   const int out_width = a.heads * a.vdim;
-  if (chunks > 0) fill(0, 0);
+  // STAGES - 1 chunks are on their way while one is worked on (a long prompt: the rows come from L2 or memory, a
+  // microsecond away, and a chunk's arithmetic is shorter than that); every round commits one group, empty or not
+  for (int ahead = 0; ahead < STAGES - 1; ++ahead) {
+    if (ahead < chunks) fill(ahead, ahead);
+    else cp_async_commit();
+  }
   for (int chunk = 0; chunk < chunks; ++chunk) {
-    int buffer = chunk & 1;
-    if (chunk + 1 < chunks) {
-      fill(chunk + 1, buffer ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    int buffer = chunk % STAGES;
+    if (chunk + STAGES - 1 < chunks) fill(chunk + STAGES - 1, (chunk + STAGES - 1) % STAGES);
+    else cp_async_commit();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
     const float* base = stage + (size_t)buffer * TOKENS * PER_TOKEN;
     const int here = min(TOKENS, count - chunk * TOKENS);
@@ -187,47 +193,84 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
     const bool writes = rg == 0 && col < a.vdim;
     int t = 0;
     if (MODE == 0) {
-      // four tokens at a time: their sums over the rows are independent of one another, so the shuffles of one
-      // hide behind the arithmetic of the next
-      for (; t + 4 <= here; t += 4) {
-        float p[4];
+      // The decayed sum's read-out does not feed the state, so its sum over the rows need not be finished token by
+      // token: every lane leaves its part in shared memory and goes on to the next token (nothing but the state's
+      // own multiply-add links two tokens); after the chunk the block adds the parts up, a thread per token and
+      // column, and writes whole pieces of rows.
+      float* parts = stage + (size_t)STAGES * TOKENS * PER_TOKEN;  // [TOKENS][16 columns][LPC + 4]
+      constexpr int PADL = LPC + 4;
+      // a group of tokens at a time: all their rows are asked of shared memory first (the loads do not depend on the
+      // state), then the state walks through them
+      constexpr int GROUP = RPL <= 8 ? 4 : 2;
+      int u = 0;
+      for (; u + GROUP <= here; u += GROUP) {
+        float4 kq[GROUP][RPL / 2];
+        float v[GROUP];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) p[u] = decayed(base + (t + u) * PER_TOKEN);
+        for (int w = 0; w < GROUP; ++w) {
+          const float* row = base + (u + w) * PER_TOKEN;
+          v[w] = row[2 * DIMP + warp * CPW + cc];
 #pragma unroll
-        for (int o = CPW; o <= 16; o <<= 1) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) p[u] += __shfl_xor_sync(0xffffffffu, p[u], o);
+          for (int j = 0; j < RPL; j += 4) {
+            kq[w][j / 2] = *reinterpret_cast<const float4*>(row + rg * RPL + j);
+            kq[w][j / 2 + 1] = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
+          }
         }
-        if (writes) {
+        const float2 dd = make_float2(decay, decay);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) out[(size_t)(t + u) * out_width] = p[u] * a.out_scale;
+        for (int w = 0; w < GROUP; ++w) {
+          const float2 vv = make_float2(v[w], v[w]);
+          float2 p = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < RPL; j += 4) {
+            float4 k4 = kq[w][j / 2], q4 = kq[w][j / 2 + 1];
+            float2 s01 = __ffma2_rn(dd, make_float2(S[j], S[j + 1]), __fmul2_rn(make_float2(k4.x, k4.y), vv));
+            float2 s23 = __ffma2_rn(dd, make_float2(S[j + 2], S[j + 3]), __fmul2_rn(make_float2(k4.z, k4.w), vv));
+            S[j] = s01.x; S[j + 1] = s01.y; S[j + 2] = s23.x; S[j + 3] = s23.y;
+            p = __ffma2_rn(s01, make_float2(q4.x, q4.y), p);
+            p = __ffma2_rn(s23, make_float2(q4.z, q4.w), p);
+          }
+          parts[((u + w) * SCAN_COLS + warp * CPW + cc) * PADL + rg] = p.x + p.y;
         }
       }
+      for (; u < here; ++u)
+        parts[(u * SCAN_COLS + warp * CPW + cc) * PADL + rg] = decayed(base + u * PER_TOKEN);
+      __syncthreads();
+      for (int i = tid; i < here * SCAN_COLS; i += SCAN_THREADS) {
+        int u = i / SCAN_COLS, c = i % SCAN_COLS;
+        const float4* mine = reinterpret_cast<const float4*>(parts + i * PADL);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < LPC / 4; ++j) {
+          float4 p4 = mine[j];
+          sum += (p4.x + p4.y) + (p4.z + p4.w);
+        }
+        if (col0 + c < a.vdim)
+          a.out[(size_t)(first + chunk * TOKENS + u) * out_width + head * a.vdim + col0 + c] = sum * a.out_scale;
+      }
+      t = here;
     }
-    for (; t < here; ++t) {
+    for (; t < here; ++t) {  // (the delta rule: its sums over the rows feed the state, token by token)
       const float* row = base + t * PER_TOKEN;
       float o;
-      if (MODE == 0) {
-        float p = decayed(row);
-#pragma unroll
-        for (int o2 = CPW; o2 <= 16; o2 <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o2);
-        o = p * a.out_scale;
-      } else {
+      {
         float v = row[2 * DIMP + warp * CPW + cc];
         float g = row[2 * DIMP + SCAN_COLS], beta = row[2 * DIMP + SCAN_COLS + 1], kq = row[2 * DIMP + SCAN_COLS + 2];
-        float kk[RPL];
-        float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f;  // S^T k and S^T q of the state before this token
+        float2 kk[RPL / 2];
+        float2 sk2 = make_float2(0.f, 0.f), sq2 = make_float2(0.f, 0.f);  // S^T k and S^T q before this token
 #pragma unroll
         for (int j = 0; j < RPL; j += 4) {
           float4 k4 = *reinterpret_cast<const float4*>(row + rg * RPL + j);
           float4 q4 = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
-          kk[j] = k4.x; kk[j + 1] = k4.y; kk[j + 2] = k4.z; kk[j + 3] = k4.w;
-          sk0 = fmaf(S[j], k4.x, sk0); sq0 = fmaf(S[j], q4.x, sq0);
-          sk1 = fmaf(S[j + 1], k4.y, sk1); sq1 = fmaf(S[j + 1], q4.y, sq1);
-          sk0 = fmaf(S[j + 2], k4.z, sk0); sq0 = fmaf(S[j + 2], q4.z, sq0);
-          sk1 = fmaf(S[j + 3], k4.w, sk1); sq1 = fmaf(S[j + 3], q4.w, sq1);
+          kk[j / 2] = make_float2(k4.x, k4.y);
+          kk[j / 2 + 1] = make_float2(k4.z, k4.w);
+          float2 s01 = make_float2(S[j], S[j + 1]), s23 = make_float2(S[j + 2], S[j + 3]);
+          sk2 = __ffma2_rn(s01, kk[j / 2], sk2);
+          sq2 = __ffma2_rn(s01, make_float2(q4.x, q4.y), sq2);
+          sk2 = __ffma2_rn(s23, kk[j / 2 + 1], sk2);
+          sq2 = __ffma2_rn(s23, make_float2(q4.z, q4.w), sq2);
         }
-        float sk = sk0 + sk1, sq = sq0 + sq1;
+        float sk = sk2.x + sk2.y, sq = sq2.x + sq2.y;
 #pragma unroll
         for (int o2 = CPW; o2 <= 16; o2 <<= 1) {
           sk += __shfl_xor_sync(0xffffffffu, sk, o2);
@@ -236,12 +279,16 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
         // (g S + k u^T)^T q = g S^T q + u (k . q): the read-out of the state after the write, without a second sum
         float u = beta * (v - g * sk);
         o = fmaf(g, sq, u * kq);
+        const float2 uu = make_float2(u, u), gg = make_float2(g, g);
 #pragma unroll
-        for (int j = 0; j < RPL; ++j) S[j] = fmaf(kk[j], u, g * S[j]);
+        for (int j = 0; j < RPL; j += 2) {
+          float2 next = __ffma2_rn(kk[j / 2], uu, __fmul2_rn(gg, make_float2(S[j], S[j + 1])));
+          S[j] = next.x; S[j + 1] = next.y;
+        }
       }
       if (writes) out[(size_t)t * out_width] = o;
     }
-    __syncthreads();  // the stage is filled again two rounds on
+    __syncthreads();  // the stage is filled again in the next round
   }
 #pragma unroll
   for (int j = 0; j < RPL; j += 4)
@@ -249,8 +296,23 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
       *reinterpret_cast<float4*>(my_state + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
 }
 
+template <int RPL, int LPC, int MODE, int TOKENS, int STAGES>
+static int launch_scan_case(const ScanArgs& a, dim3 grid, cudaStream_t stream) {
+  size_t bytes = (size_t)STAGES * TOKENS * (2 * RPL * LPC + SCAN_COLS + 4) * sizeof(float);
+  if (MODE == 0) bytes += (size_t)TOKENS * SCAN_COLS * (LPC + 4) * sizeof(float);  // the parts of the read-out
+  static bool allowed = false;  // (more than 48 KB of dynamic shared memory has to be asked for once)
+  if (bytes > 48 * 1024 && !allowed) {
+    if (cudaFuncSetAttribute(scan_kernel<RPL, LPC, MODE, TOKENS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)bytes) != cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    allowed = true;
+  }
+  return dllm_launch_pdl(scan_kernel<RPL, LPC, MODE, TOKENS, STAGES>, grid, dim3(SCAN_COLS * LPC), bytes, stream, a);
+}
+
+// `longest`: the most new tokens a sequence of the step has (the host knows; the kernel reads the real counts).
 template <int MODE>
-static int launch_scan(const ScanArgs& a, int sequences, cudaStream_t stream) {
+static int launch_scan(const ScanArgs& a, int sequences, int longest, cudaStream_t stream) {
   dim3 grid((a.vdim + SCAN_COLS - 1) / SCAN_COLS, a.heads, sequences);
   // Lanes a column: 8 where the step has blocks enough to give every scheduler several warps (many sequences or
   // heads), else 16, which doubles the warps (measured on one prompt of 2,048 tokens, 16 heads of 128 x 128: 477 us
@@ -258,11 +320,11 @@ static int launch_scan(const ScanArgs& a, int sequences, cudaStream_t stream) {
   long long blocks = (long long)grid.x * grid.y * grid.z;
   int dimp = a.dim <= 32 ? 32 : (a.dim <= 64 ? 64 : (a.dim <= 128 ? 128 : 256));
   int lanes = (blocks * 4 >= 148 * 16 || dimp / 16 < 4) ? 8 : 16;
-#define SCAN_CASE(RPL, LPC, TOKENS)                                                                               \
-  if (dimp == RPL * LPC && lanes == LPC) {                                                                        \
-    size_t bytes = 2 * (size_t)TOKENS * (2 * RPL * LPC + SCAN_COLS + 4) * sizeof(float);                          \
-    return dllm_launch_pdl(scan_kernel<RPL, LPC, MODE, TOKENS>, grid, dim3(SCAN_COLS * LPC), bytes, stream, a);   \
-  }
+  bool deep = longest > 32;  // four stages for prompts, two for steps of single tokens and short portions
+#define SCAN_CASE(RPL, LPC, TOKENS)                                                                 \
+  if (dimp == RPL * LPC && lanes == LPC)                                                            \
+    return deep ? launch_scan_case<RPL, LPC, MODE, TOKENS, 4>(a, grid, stream)                      \
+                : launch_scan_case<RPL, LPC, MODE, TOKENS, 2>(a, grid, stream);
   SCAN_CASE(4, 8, 16)
   SCAN_CASE(8, 8, 16) SCAN_CASE(4, 16, 16)
   SCAN_CASE(16, 8, 16) SCAN_CASE(8, 16, 16)
@@ -285,7 +347,7 @@ static int scan_vector(const float* q, const float* k, const float* v, int strid
 // times: the sums are linear in them, so the state holds the unscaled sum and the read-out is multiplied instead.
 DLLM_EXPORT int dllm_decay_scan(const float* q, const float* k, const float* v, int stride, int heads, int dim,
                                 int vdim, const float* decay, float k_scale, float* state,
-                                const int* cu_seqlens, const int* slots, int sequences, float* out,
+                                const int* cu_seqlens, const int* slots, int sequences, int longest, float* out,
                                 cudaStream_t stream) {
   if (sequences <= 0) return DLLM_OK;
   if (!scan_sizes_ok(heads, heads, dim, vdim, stride) || sequences >= 65536) return DLLM_UNSUPPORTED_SIZE;
@@ -294,7 +356,7 @@ DLLM_EXPORT int dllm_decay_scan(const float* q, const float* k, const float* v, 
   a.q = q; a.k = k; a.v = v; a.stride = stride; a.heads = heads; a.qk_heads = heads; a.dim = dim; a.vdim = vdim;
   a.state = state; a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.decay = decay;
   a.out_scale = k_scale; a.vector = scan_vector(q, k, v, stride, dim, vdim);
-  return launch_scan<0>(a, sequences, stream);
+  return launch_scan<0>(a, sequences, longest, stream);
 }
 
 // The gated delta rule over the new tokens of every sequence. q and k are unit vectors (q scaled) per q/k head, v
@@ -302,7 +364,7 @@ DLLM_EXPORT int dllm_decay_scan(const float* q, const float* k, const float* v, 
 // step sizes beta and the q/k heads' k.q (see `dllm_delta_prepare`).
 DLLM_EXPORT int dllm_delta_scan(const float* q, const float* k, const float* v, int stride, int heads, int qk_heads,
                                 int dim, int vdim, const float* aux, int aux_stride, float* state,
-                                const int* cu_seqlens, const int* slots, int sequences, float* out,
+                                const int* cu_seqlens, const int* slots, int sequences, int longest, float* out,
                                 cudaStream_t stream) {
   if (sequences <= 0) return DLLM_OK;
   if (!scan_sizes_ok(heads, qk_heads, dim, vdim, stride) || sequences >= 65536) return DLLM_UNSUPPORTED_SIZE;
@@ -311,7 +373,7 @@ DLLM_EXPORT int dllm_delta_scan(const float* q, const float* k, const float* v, 
   a.q = q; a.k = k; a.v = v; a.stride = stride; a.heads = heads; a.qk_heads = qk_heads; a.dim = dim; a.vdim = vdim;
   a.state = state; a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.aux = aux; a.aux_stride = aux_stride;
   a.out_scale = 1.0f; a.vector = scan_vector(q, k, v, stride, dim, vdim);
-  return launch_scan<1>(a, sequences, stream);
+  return launch_scan<1>(a, sequences, longest, stream);
 }
 
 // ---- what the delta rule needs of a token before its scan --------------------------------------------------------

@@ -31,10 +31,10 @@ _prototypes = {
                                                 c_float, c_void_p],
     ("elementwise", "dllm_concat_restart"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "dllm_decay_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                                       c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                       c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     ("recurrent", "dllm_silu_columns"): [c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "dllm_delta_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
-                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     ("recurrent", "dllm_delta_prepare"): [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_int, c_void_p],
@@ -276,7 +276,7 @@ def decay_scan(out: torch.Tensor, rows: torch.Tensor, q_at: int, k_at: int, v_at
     _check(_fn("recurrent", "dllm_decay_scan")(
         _columns(rows, q_at), _columns(rows, k_at), _columns(rows, v_at), rows.shape[1], heads, dim, vdim,
         decay.data_ptr(), float(k_scale), state.data_ptr(), batch.cu_seqlens.data_ptr(),
-        batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(), _stream()), "decay_scan",
+        batch.slots.data_ptr(), batch.n_seqs, int(batch.max_new), out.data_ptr(), _stream()), "decay_scan",
         lambda: f"dim={dim} (a multiple of 4, at most 256)")
 
 
@@ -315,7 +315,8 @@ def delta_scan(out: torch.Tensor, prepared: torch.Tensor, aux: torch.Tensor, hea
     _check(_fn("recurrent", "dllm_delta_scan")(
         prepared.data_ptr(), _columns(prepared, qk_heads * dim), _columns(prepared, 2 * qk_heads * dim),
         prepared.shape[1], heads, qk_heads, dim, vdim, aux.data_ptr(), aux.shape[1], state.data_ptr(),
-        batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, out.data_ptr(), _stream()), "delta_scan",
+        batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, int(batch.max_new), out.data_ptr(),
+        _stream()), "delta_scan",
         lambda: f"dim={dim} (a multiple of 4, at most 256)")
 
 
