@@ -400,8 +400,8 @@ DLLM_EXPORT int dllm_layernorm(void* out, const float* x, const float* weight, c
 }
 
 // ---- gated unit with clamped inputs ------------------------------------------------------------------------------
-// in[r] = [gate (width values) | up (width values)] as the product left them; g = min(gate, limit), u = clamp(up,
-// -limit, limit); out[r, i] = g * sigmoid(alpha * g) * (u + shift), computed in float32, rounded once.
+// in[r] = gate_0, up_0, gate_1, up_1, ... as the product of the interleaved weight left them; g = min(gate, limit),
+// u = clamp(up, -limit, limit); out[r, i] = g * sigmoid(alpha * g) * (u + shift), computed in float32, rounded once.
 template <typename T>
 __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ in, long long total, int width,
                                    float limit, float alpha, float shift) {
@@ -411,8 +411,8 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ in
        i += (long long)gridDim.x * blockDim.x) {
     long long r = i / width;
     int c = (int)(i - r * width);
-    float g = fminf(to_float(in[r * 2 * width + c]), limit);
-    float u = fminf(fmaxf(to_float(in[r * 2 * width + width + c]), -limit), limit);
+    float g = fminf(to_float(in[r * 2 * width + 2 * c]), limit);
+    float u = fminf(fmaxf(to_float(in[r * 2 * width + 2 * c + 1]), -limit), limit);
     float s = 1.0f / (1.0f + expf(-alpha * g));
     out[i] = from_float<T>(g * s * (u + shift));
   }

@@ -22,6 +22,10 @@
 // features writes its largest value per token and the feature that has it (the lowest on ties) as a candidate,
 // C = [tokens][tiles](value, feature as an int's bits); a second small kernel picks each token's winner.
 #define EPI_ARGMAX 9
+// W's rows interleave gate and up as for SwiGLU; C in the activation type [M,N/2] = g * sigmoid(1.702 g) * (u + 1)
+// with g = min(gate, limit), u = clamp(up, -limit, limit), `limit` a launch argument. The weight-streaming kernels
+// (at most 64 rows) have it; larger steps store gate and up and apply `glu_clamped_kernel`.
+#define EPI_GLU_CLAMPED 10
 
 // What the q/k/v epilogue needs: where queries go, where the cache is, the rotation table, who the tokens are.
 struct RopeArgs {
@@ -94,8 +98,14 @@ template <typename T> __device__ __forceinline__ float silu_for(float g) { retur
 template <> __device__ __forceinline__ float silu_for<__nv_bfloat16>(float g) { return silu_fast(g); }
 
 // Stores the pair of adjacent columns (n, n+1) of row m. n is even.
+__device__ __forceinline__ float glu_clamped(float gate, float up, float limit) {
+  float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+}
+
 template <int EPI, typename T>
-__device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n, int M, int N, float v0, float v1) {
+__device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n, int M, int N, float v0, float v1,
+                                              float limit = 0.f) {
   if (m >= M || n >= N) return;
   bool second = n + 1 < N;
   if (EPI == EPI_STORE_F32) {
@@ -110,6 +120,9 @@ __device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n
     float* dst = (float*)c + (size_t)m * N + n;
     dst[0] += v0;
     if (second) dst[1] += v1;
+  } else if (EPI == EPI_GLU_CLAMPED) {
+    T* dst = (T*)c + (size_t)m * (N / 2) + (n >> 1);
+    dst[0] = from_float<T>(glu_clamped(v0, v1, limit));
   } else {
     T* dst = (T*)c + (size_t)m * (N / 2) + (n >> 1);
     dst[0] = from_float<T>(silu_for<T>(v0) * v1);
@@ -153,7 +166,7 @@ __device__ __forceinline__ void epilogue_row16(void* __restrict__ c, int m, int 
       dst[1] = hi;
       return;
     }
-  } else {  // SwiGLU: eight outputs
+  } else if (EPI == EPI_SWIGLU) {  // eight outputs
     if (whole && (N & 15) == 0 && sizeof(T) == 2) {
       uint4 o;
       __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);

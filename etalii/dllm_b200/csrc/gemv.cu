@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
         if (n < N && v0 > best_value) { best_value = v0; best_feature = n; }
         if (n + 1 < N && v1 > best_value) { best_value = v1; best_feature = n + 1; }
       } else {
-        epilogue_pair<EPI, bf16>(c, m, item * TILE + 2 * p, M, N, v0, v1);
+        epilogue_pair<EPI, bf16>(c, m, item * TILE + 2 * p, M, N, v0, v1, eps);  // (eps: the limit of a clamped GLU)
       }
     }
     if (EPI == EPI_ARGMAX) {  // (at most one item a thread: the launch gives 8 * NT * 8 threads or more)
@@ -373,6 +373,7 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
     case EPI_SWIGLU: return launch<EPI_SWIGLU, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     case EPI_QKV_ROPE: return launch<EPI_QKV_ROPE, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     case EPI_ARGMAX: return launch<EPI_ARGMAX, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
+    case EPI_GLU_CLAMPED: return launch<EPI_GLU_CLAMPED, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -385,8 +386,10 @@ DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, floa
                                int K, int epilogue, const void* prefetch_ptr, long long prefetch_bytes,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 ||
-      (epilogue > EPI_SWIGLU && epilogue != EPI_ARGMAX))
+  bool gated = epilogue == EPI_SWIGLU || epilogue == EPI_GLU_CLAMPED;
+  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && gated) || epilogue < 0 ||
+      (epilogue > EPI_SWIGLU && epilogue != EPI_ARGMAX && epilogue != EPI_GLU_CLAMPED) ||
+      (epilogue == EPI_GLU_CLAMPED && norm_w != nullptr))
     return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{};
   Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};

@@ -69,7 +69,8 @@ struct Unit {
       }
     }
   }
-  __device__ __forceinline__ void finish(void* c, int M, int N, const RopeArgs& rope, float v0, float v1) const {
+  __device__ __forceinline__ void finish(void* c, int M, int N, const RopeArgs& rope, float v0, float v1,
+                                         float limit) const {
     if (EPI == EPI_QKV_ROPE) {
       int hd = rope.cache.head_dim, nkv = rope.cache.kv_heads, heads = rope.heads;
       int d0 = dim0 + p, d1 = d0 + 8;
@@ -96,7 +97,7 @@ struct Unit {
       if (n < N) dst[0] = r0 + v0;
       if (n + 1 < N) dst[1] = r1 + v1;
     } else {
-      epilogue_pair<EPI, bf16>(c, m, item * TILE + 2 * p, M, N, v0, v1);
+      epilogue_pair<EPI, bf16>(c, m, item * TILE + 2 * p, M, N, v0, v1, limit);
     }
   }
 };
@@ -303,7 +304,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
       v0 *= inv;
       v1 *= inv;
     }
-    unit.finish(c, M, N, rope, v0, v1);
+    unit.finish(c, M, N, rope, v0, v1, eps);  // (eps: the limit of a clamped GLU, which takes no norm)
   };
   if (tid < units) finish(tid, early[0]);
   if (tid + WARPS * 32 < units) finish(tid + WARPS * 32, early[1]);
@@ -386,6 +387,7 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
     case EPI_RESIDUAL: return launch<EPI_RESIDUAL, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
     case EPI_SWIGLU: return launch<EPI_SWIGLU, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
     case EPI_QKV_ROPE: return launch<EPI_QKV_ROPE, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
+    case EPI_GLU_CLAMPED: return launch<EPI_GLU_CLAMPED, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -399,7 +401,9 @@ DLLM_EXPORT int dllm_gemv_cluster(void* c, const void* a, const float* norm_w, f
                                   int K, int epilogue, int cluster, const void* prefetch_ptr, long long prefetch_bytes,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 || epilogue > EPI_SWIGLU)
+  bool gated = epilogue == EPI_SWIGLU || epilogue == EPI_GLU_CLAMPED;
+  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && gated) || epilogue < 0 ||
+      (epilogue > EPI_SWIGLU && epilogue != EPI_GLU_CLAMPED) || (epilogue == EPI_GLU_CLAMPED && norm_w != nullptr))
     return DLLM_UNSUPPORTED_SIZE;
   if (cluster < 0) return DLLM_BAD_ARGUMENT;
   int blocks = cluster;

@@ -11,9 +11,12 @@ import torch
 from .build import library
 
 EPI_STORE_F32, EPI_STORE_T, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+EPI_GLU_CLAMPED = 10
+"""W interleaves gate and up rows; c[M,N/2] = g sigmoid(1.702 g) (u + 1) with g = min(gate, limit), u = clamp(up,
+-limit, limit). Only the weight-streaming kernels have it (`glu_clamped_fuses`); `eps` carries the limit."""
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _STATUS = {-1: "bad argument", -2: "unsupported size", -3: "kernel launch failed"}
-_EPILOGUE_NAMES = {0: "store_f32", 1: "store", 2: "residual", 3: "swiglu"}
+_EPILOGUE_NAMES = {0: "store_f32", 1: "store", 2: "residual", 3: "swiglu", 10: "glu_clamped"}
 
 
 class KernelError(RuntimeError):
@@ -217,9 +220,16 @@ def layernorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: flo
                                                 float(eps), _code(out.dtype), _stream()), "layernorm")
 
 
+def glu_clamped_fuses(rows: int, outputs: int, inner: int) -> bool:
+    """Whether a bfloat16 product of these sizes runs in one of the two weight-streaming kernels that can end in the
+    clamped GLU (a block per 16 rows of W, or the reduction split over a cluster)."""
+    return streams(rows, outputs, inner) and not takes_weights_as_rows(rows, outputs, inner) and \
+        not streams_through_shared_memory(rows, outputs, inner)
+
+
 def glu_clamped(out: torch.Tensor, gate_up: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
-    """gate_up [rows, 2 width] = [gate | up]; out[rows, width] = g sigmoid(alpha g) (u + shift) with g = min(gate,
-    limit), u = clamp(up, -limit, limit), in float32, rounded once."""
+    """gate_up [rows, 2 width] = gate_0, up_0, gate_1, up_1, ...; out[rows, width] = g sigmoid(alpha g) (u + shift)
+    with g = min(gate, limit), u = clamp(up, -limit, limit), in float32, rounded once."""
     _cuda(out, gate_up)
     rows, width = out.shape
     assert gate_up.shape == (rows, 2 * width) and gate_up.dtype == out.dtype
@@ -538,7 +548,9 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k, (a.shape, w.shape)
-    want_cols = n // 2 if epilogue == EPI_SWIGLU else n
+    want_cols = n // 2 if epilogue in (EPI_SWIGLU, EPI_GLU_CLAMPED) else n
+    if epilogue == EPI_GLU_CLAMPED:
+        assert w.dtype == torch.bfloat16 and kernel == 0 and norm_weight is None and glu_clamped_fuses(m, n, k)
     want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else w.dtype
     assert tuple(c.shape) == (m, want_cols) and c.dtype == want_dtype, (c.shape, c.dtype, m, want_cols, want_dtype)
     def detail() -> str:

