@@ -385,10 +385,68 @@ __global__ void layernorm_kernel(T* __restrict__ out, const float* __restrict__ 
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<T>((src[i] - mean) * inv * weight[i]);
 }
 
+// Narrow rows (hidden a multiple of 4, at most 4096 floats): one warp per row, the row kept in registers between the
+// mean, the squared deviations and the scaling (one pass over memory), 16-byte loads, sums in a fixed tree.
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_warp_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                             const float* __restrict__ weight,
+                                                             const int* __restrict__ rows, int n_rows, int hidden,
+                                                             float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int lane = threadIdx.x & 31;
+  int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
+  int vecs = hidden >> 2;
+  float4 v[32];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < vecs) {
+      v[i] = src[idx];
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  float mean = warp_sum(sum) / (float)hidden;
+  float squares = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < vecs) {
+      v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+      squares = fmaf(v[i].x, v[i].x, squares); squares = fmaf(v[i].y, v[i].y, squares);
+      squares = fmaf(v[i].z, v[i].z, squares); squares = fmaf(v[i].w, v[i].w, squares);
+    }
+  }
+  float inv = 1.0f / sqrtf(warp_sum(squares) / (float)hidden + eps);
+  const float4* wv = reinterpret_cast<const float4*>(weight);
+  T* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < vecs) {
+      float4 w4 = wv[idx];
+      store4(dst + 4 * idx, v[i].x * inv * w4.x, v[i].y * inv * w4.y, v[i].z * inv * w4.z, v[i].w * inv * w4.w);
+    }
+  }
+}
+
 DLLM_EXPORT int dllm_layernorm(void* out, const float* x, const float* weight, const int* rows, int n_rows, int hidden,
                                float eps, int out_dtype, cudaStream_t stream) {
   if (n_rows <= 0) return DLLM_OK;
   if (hidden <= 0) return DLLM_BAD_ARGUMENT;
+  if ((hidden & 3) == 0 && hidden <= 4096) {  // whatever the number of rows, so a row has the same bits everywhere
+    int blocks = (n_rows + 7) / 8;
+    if (out_dtype == DLLM_F32)
+      return dllm_launch_pdl(layernorm_warp_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, x, weight,
+                             rows, n_rows, hidden, eps);
+    if (out_dtype == DLLM_BF16)
+      return dllm_launch_pdl(layernorm_warp_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                             (__nv_bfloat16*)out, x, weight, rows, n_rows, hidden, eps);
+    return DLLM_BAD_ARGUMENT;
+  }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (out_dtype == DLLM_F32)
     return dllm_launch_pdl(layernorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (float*)out, x, weight,
@@ -418,18 +476,64 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ in
   }
 }
 
+// Four outputs a thread from eight inputs (width a multiple of 4: rows start on 16 bytes).
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(pairs[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <typename T>
+__global__ void glu_clamped_vector_kernel(T* __restrict__ out, const T* __restrict__ in, long long quads, float limit,
+                                          float alpha, float shift) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads;
+       i += (long long)gridDim.x * blockDim.x) {
+    float v[8], y[4];
+    load8(in + 8 * i, v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float g = fminf(v[2 * j], limit);
+      float u = fminf(fmaxf(v[2 * j + 1], -limit), limit);
+      y[j] = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
+    }
+    store4(out + 4 * i, y[0], y[1], y[2], y[3]);
+  }
+}
+
+template <typename T>
+static int launch_glu_clamped(T* out, const T* in, int rows, int width, float limit, float alpha, float shift,
+                              cudaStream_t stream) {
+  long long total = (long long)rows * width;
+  if ((width & 3) == 0) {
+    long long quads = total / 4;
+    int blocks = (int)((quads + 255) / 256 < 148 * 16 ? (quads + 255) / 256 : 148 * 16);
+    return dllm_launch_pdl(glu_clamped_vector_kernel<T>, dim3(blocks), dim3(256), 0, stream, out, in, quads, limit,
+                           alpha, shift);
+  }
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  return dllm_launch_pdl(glu_clamped_kernel<T>, dim3(blocks), dim3(256), 0, stream, out, in, total, width, limit, alpha,
+                         shift);
+}
+
 DLLM_EXPORT int dllm_glu_clamped(void* out, const void* in, int rows, int width, float limit, float alpha, float shift,
                                  int dtype, cudaStream_t stream) {
   if (rows <= 0) return DLLM_OK;
   if (width <= 0 || out == nullptr || in == nullptr) return DLLM_BAD_ARGUMENT;
-  long long total = (long long)rows * width;
-  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == DLLM_F32)
-    return dllm_launch_pdl(glu_clamped_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out,
-                           (const float*)in, total, width, limit, alpha, shift);
+    return launch_glu_clamped((float*)out, (const float*)in, rows, width, limit, alpha, shift, stream);
   if (dtype == DLLM_BF16)
-    return dllm_launch_pdl(glu_clamped_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
-                           (const __nv_bfloat16*)in, total, width, limit, alpha, shift);
+    return launch_glu_clamped((__nv_bfloat16*)out, (const __nv_bfloat16*)in, rows, width, limit, alpha, shift, stream);
   return DLLM_BAD_ARGUMENT;
 }
 

@@ -92,7 +92,7 @@ def _inputs(dtype, width, seed):
 
 
 @pytest.mark.parametrize("name,dtype", DTYPES)
-@pytest.mark.parametrize("width", [72, 1000])
+@pytest.mark.parametrize("width", [72, 1000, 4100])
 def test_layer_norm_part(name, dtype, width):
     from etalii.dllm_b200.parts import PartSpec, build_part
 
