@@ -549,3 +549,37 @@ def test_trace_replay_of_a_random_model(tmp_path):
     last = np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1)
     assert not (out / "1.f32").exists()
     assert rel_error(first, want[[0, 16]]) <= TOL["float32"] and rel_error(last, want[[19]]) <= TOL["float32"]
+
+
+def test_command_line_on_a_tisalorn_folder(tmp_path):
+    """`dllm-b200 random` writes a Tisalorn folder from a config.json, `info` reads it back, `generate` continues a
+    prompt greedily in float32 with the tokens the plain implementation chooses from the same folder's weights."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from etalii.dllm_b200.weights.safetensors_io import SafetensorsFile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tool = [sys.executable, os.path.join(root, "bin", "dllm-b200")]
+    config = C.CASES["plain_order"]()
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    folder = str(tmp_path / "model")
+    done = subprocess.run(tool + ["random", "--config", str(tmp_path / "config.json"), "--seed", "4", "--out", folder,
+                                  "--std", "0.2"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    done = subprocess.run(tool + ["--model", folder, "info"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0 and json.loads(done.stdout)["architecture"] == "Tisalorn"
+    prompt = C.tokens_for(config, [9], seed=13)[0]
+    done = subprocess.run(tool + ["--model", folder, "--dtype", "float32", "--cache-tokens", "256", "generate",
+                                  "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "6", "--ignore-eos"],
+                          capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stderr[-2000:]
+    got = [int(t) for t in done.stdout.split()]
+    handle = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    plain = P.PlainTisalorn(config, {name: handle.tensor(name) for name in handle.names()})
+    history = list(prompt)
+    for _ in range(6):
+        history.append(int(np.argmax(plain.forward(history, {})[0][-1].numpy())))
+    assert got == history[len(prompt):]
