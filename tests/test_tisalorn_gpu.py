@@ -407,7 +407,7 @@ def _compare(case, got, prompts, dtype_name):
     its own root mean square, which at a sequence's first tokens can be a number near zero whose sign rounding
     decides, so single positions may differ by more than rounding elsewhere; there 9 of 10 positions must be within
     the tolerance and the median position within a third of it (the tests with many short requests have many first
-    tokens). (What a lost key or a stale state does is judged in
+    tokens). (What a lost key or a stale state does is decided in
     float32, where the same schedules run through the same cache and step function.)"""
     errors = []
     for rows, tokens in zip(got, prompts):
