@@ -29,8 +29,10 @@ from .allocators import CacheError, FreeList
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What one cache entry needs. kind "kv": keys and values of `kv_heads` x `head_dim` per position, all of them
-    (window None) or the last `window`. kind "state": a float32 tensor of `state_shape` per sequence. kind
+    """What one cache entry needs. kind "kv": keys and values of `kv_heads` x `head_dim` per position (values of
+    `value_dim` where that is given and differs), all of them (window None), the last `window`, or those of the
+    running chunk of `chunk` positions (a mixer whose tokens only look back to the start of their own chunk: positions
+    of chunks that are over are never read again). kind "state": a float32 tensor of `state_shape` per sequence. kind
     "several": a mixer that keeps more than one thing (keys and values beside a state, two states) lists them in
     `parts`; the model gives every part a cache entry of its own and hands the mixer their views in that order."""
 
@@ -40,16 +42,21 @@ class CacheNeed:
     window: int | None = None
     state_shape: tuple[int, ...] = ()
     parts: tuple["CacheNeed", ...] = ()
+    value_dim: int = 0
+    chunk: int | None = None
 
 
 class KvView:
     """What a kernel needs to address one cache entry."""
 
     __slots__ = ("base_ptr", "storage", "page_table", "max_pages", "page_size", "kv_heads", "head_dim", "dtype",
-                 "window")
+                 "window", "value_dim")
 
-    def __init__(self, storage, page_table, page_size, kv_heads, head_dim, window):
-        self.storage = storage  # [pages, 2, kv_heads, page_size, head_dim]
+    def __init__(self, storage, page_table, page_size, kv_heads, head_dim, window, value_dim=0):
+        # [pages, 2, kv_heads, page_size, head_dim]; with values of another size than the keys a page is
+        # [keys: kv_heads, page_size, head_dim | values: kv_heads, page_size, value_dim], stored flat
+        self.storage = storage
+        self.value_dim = value_dim or head_dim
         self.base_ptr = storage.data_ptr()
         self.page_table = page_table
         self.max_pages = page_table.shape[1]
@@ -70,8 +77,11 @@ class _KvGroup:
         self.storage = self.table = None
         if device is not None:
             # zeros, not garbage: a blockwise kernel multiplies masked rows of a page by probability 0
-            self.storage = torch.zeros((len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim),
-                                       dtype=dtype, device=device)
+            if need.value_dim in (0, need.head_dim):
+                shape = (len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim)
+            else:
+                shape = (len(entries), n_pages, need.kv_heads * page_size * (need.head_dim + need.value_dim))
+            self.storage = torch.zeros(shape, dtype=dtype, device=device)
             self.table = torch.zeros((n_slots, max_pages), dtype=torch.int32, device=device)
         self.dirty: set[int] = set()
 
@@ -112,6 +122,10 @@ class PagedCache:
                 raise CacheError(f"unknown cache kind {need.kind!r}")
         for need, entries in by_need.items():
             pages = self.n_pages
+            if need.chunk and not need.window:
+                # (as for a window below: every slot's running chunk, and one whole prompt on top)
+                per_sequence = -(-need.chunk // self.page_size) + 1
+                pages = min(self.n_pages, per_sequence * self.n_slots + -(-self.max_length // self.page_size))
             if need.window:
                 # A windowed group holds at most the window (plus the page being filled) per sequence while it
                 # decodes; but a whole prompt enters in one step and needs all its positions at once, so there is
@@ -161,6 +175,10 @@ class PagedCache:
             first_needed = 0
             if group.need.window:  # positions below (start + 1 - window) are never read again
                 first_needed = max(0, (self.lengths[slot] + 1 - group.need.window)) // self.page_size
+            if group.need.chunk:  # nor are those before the chunk that the first new position lies in
+                first_needed = max(first_needed,
+                                   (self.lengths[slot] // group.need.chunk) * group.need.chunk // self.page_size)
+            if first_needed:
                 for index in range(min(first_needed, len(have))):
                     if have[index] is not None:
                         group.pool.give([have[index]])
@@ -228,7 +246,7 @@ class PagedCache:
     def kv_view(self, entry: int) -> KvView:
         group, index = self._where[entry]
         return KvView(group.storage[index], group.table, self.page_size, group.need.kv_heads, group.need.head_dim,
-                      group.need.window)
+                      group.need.window, group.need.value_dim)
 
     def state(self, entry: int) -> torch.Tensor:
         """The fixed-size state of entry `entry`: [slots, *state_shape] float32."""

@@ -567,6 +567,57 @@ DLLM_EXPORT int dllm_norm_sum_residual(float* residual, const float* a, const fl
                          eps, factor);
 }
 
+// ---- one RMS-normed sublayer output into the residual -------------------------------------------------------------
+// residual[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w, everything float32; one block per row. The arrangement that
+// norms a sublayer's output instead of its input ends both of its sublayers with this.
+__global__ void norm_add_residual_kernel(float* __restrict__ residual, const float* __restrict__ y,
+                                         const float* __restrict__ w, int hidden, float eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t base = (size_t)blockIdx.x * hidden;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = y[base + i];
+    s = fmaf(v, v, s);
+  }
+  float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) residual[base + i] += y[base + i] * inv * w[i];
+}
+
+DLLM_EXPORT int dllm_norm_add_residual(float* residual, const float* y, const float* w, int rows, int hidden, float eps,
+                                       cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (hidden <= 0 || residual == nullptr || y == nullptr || w == nullptr) return DLLM_BAD_ARGUMENT;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  return dllm_launch_pdl(norm_add_residual_kernel, dim3(rows), dim3(threads), 0, stream, residual, y, w, hidden, eps);
+}
+
+// ---- the float32 stream as an operand: out = bfloat16(x) ----------------------------------------------------------
+// For a sublayer that reads the stream itself, with no norm in front whose kernel would do the rounding.
+__global__ void cast_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ x, long long pairs,
+                                 long long total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs;
+       i += (long long)gridDim.x * blockDim.x) {
+    if (2 * i + 1 < total) {
+      float2 v = *reinterpret_cast<const float2*>(x + 2 * i);
+      *reinterpret_cast<__nv_bfloat162*>(out + 2 * i) = __floats2bfloat162_rn(v.x, v.y);
+    } else {
+      out[2 * i] = __float2bfloat16_rn(x[2 * i]);
+    }
+  }
+}
+
+DLLM_EXPORT int dllm_cast_rows(void* out, const float* x, long long total, cudaStream_t stream) {
+  if (total <= 0) return DLLM_OK;
+  if (out == nullptr || x == nullptr || ((uintptr_t)x & 7) || ((uintptr_t)out & 3)) return DLLM_BAD_ARGUMENT;
+  long long pairs = (total + 1) / 2;
+  int blocks = (int)((pairs + 255) / 256 < 148 * 16 ? (pairs + 255) / 256 : 148 * 16);
+  return dllm_launch_pdl(cast_rows_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, x, pairs, total);
+}
+
 // ---- the stream beside a kept copy, as one operand ---------------------------------------------------------------
 // both[r] = [x[r] | kept[r]] in the activation type (the operand of the product that mixes the two), and then
 // x[r] = start (one row for all): the product adds into x in its epilogue, so x ends as start + W [x | kept].

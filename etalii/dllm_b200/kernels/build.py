@@ -36,6 +36,8 @@ SOURCES = {
     "attention_prefill_tcgen05": "attention_prefill_tcgen05.cu",
     "attention_decode_static": "attention_decode_static.cu",
     "recurrent": "recurrent.cu",
+    "diff_attention": "diff_attention.cu",
+    "moe": "moe.cu",
     "sampling": "sampling.cu",
     "step_launcher": "step_launcher.cu",
 }

@@ -32,6 +32,21 @@ _prototypes = {
     ("elementwise", "dllm_glu_clamped"): [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
     ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                                 c_float, c_void_p],
+    ("elementwise", "dllm_norm_add_residual"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    ("elementwise", "dllm_cast_rows"): [c_void_p, c_void_p, c_longlong, c_void_p],
+    ("diff_attention", "dllm_map_prepare"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                             c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("diff_attention", "dllm_diff_attention"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int,
+                                                c_void_p],
+    ("moe", "dllm_moe_route"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                c_void_p],
+    ("moe", "dllm_moe_up"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_float,
+                             c_float, c_int, c_void_p],
+    ("moe", "dllm_moe_down"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                               c_int, c_void_p],
     ("elementwise", "dllm_concat_restart"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "dllm_decay_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
@@ -249,6 +264,123 @@ def norm_sum_residual(residual: torch.Tensor, a: torch.Tensor, wa: torch.Tensor,
     _check(_fn("elementwise", "dllm_norm_sum_residual")(residual.data_ptr(), a.data_ptr(), wa.data_ptr(), b.data_ptr(),
                                                         wb.data_ptr(), rows, hidden, float(eps), float(factor),
                                                         _stream()), "norm_sum_residual")
+
+
+def norm_add_residual(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """residual += y / sqrt(mean(y^2) + eps) * weight, row by row, all float32 (a sublayer whose OUTPUT is normed)."""
+    _cuda(residual, y, weight)
+    rows, hidden = y.shape
+    assert all(t.dtype == torch.float32 for t in (residual, y, weight))
+    assert residual.shape[0] >= rows and residual.shape[1] == hidden and weight.numel() == hidden
+    _check(_fn("elementwise", "dllm_norm_add_residual")(residual.data_ptr(), y.data_ptr(), weight.data_ptr(), rows,
+                                                        hidden, float(eps), _stream()), "norm_add_residual")
+
+
+def cast_rows(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out = bfloat16(x), x float32 of the same shape: the stream as the operand of a product that has no norm in
+    front."""
+    _cuda(out, x)
+    assert x.dtype == torch.float32 and out.dtype == torch.bfloat16 and out.numel() == x.numel()
+    _check(_fn("elementwise", "dllm_cast_rows")(out.data_ptr(), x.data_ptr(), x.numel(), _stream()), "cast_rows")
+
+
+def map_prepare(rows: torch.Tensor, q_at: int, k_at: int, v_at: int, q_out: torch.Tensor, cache, heads: int, dim: int,
+                q_weight: torch.Tensor, k_weight: torch.Tensor | None, eps: float, table: torch.Tensor | None,
+                rotary_dim: int, batch, write_cache: bool = True) -> None:
+    """Queries and keys of two score maps per head, from the projected rows [tokens, n] float32 (q at column q_at:
+    heads x 2 x dim; k at k_at: kv_heads x 2 x dim; v at v_at: kv_heads x value_dim): every (head, map) vector is
+    divided by its root mean square and multiplied by the weight [dim] (one for q, one for k), its first
+    `rotary_dim` places are rotated in halves by the token's position; q goes to q_out [tokens, heads x 2 x dim]
+    float32, k and v into the token's place in the cache (keys of 2 dim, values of `cache.value_dim`). With
+    `write_cache` False only the queries are made."""
+    _cuda(rows, q_out, q_weight, k_weight, table)
+    tokens = batch.n_tokens
+    assert rows.dtype == torch.float32 and q_out.dtype == torch.float32 and q_weight.dtype == torch.float32
+    assert cache.head_dim == 2 * dim and q_weight.numel() == dim and q_out.shape[1] == heads * 2 * dim
+    assert rows.shape[0] >= tokens and q_out.shape[0] >= tokens
+    assert not write_cache or (k_weight is not None and k_weight.dtype == torch.float32 and k_weight.numel() == dim)
+    if table is not None and rotary_dim > 0:
+        assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
+        assert table.shape[1] == rotary_dim // 2 and table.shape[2] == 2
+    _check(_fn("diff_attention", "dllm_map_prepare")(
+        rows.data_ptr(), rows.shape[1], int(q_at), int(k_at), int(v_at), q_out.data_ptr(), cache.base_ptr,
+        cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, dim, cache.value_dim,
+        q_weight.data_ptr(), k_weight.data_ptr() if k_weight is not None else None, float(eps),
+        table.data_ptr() if table is not None else None, int(rotary_dim) if table is not None else 0,
+        batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), tokens, 1 if write_cache else 0,
+        _code(cache.dtype), _stream()), "map_prepare",
+        lambda: f"dim={dim}, value_dim={cache.value_dim} (at most 256), rotary_dim={rotary_dim} (even, at most dim)")
+
+
+def diff_attention(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | None, gate_at: int, cache, heads: int,
+                   dim: int, scale: float, softcap: float, weight: float, eps: float, out_scale: float, chunk: int,
+                   window: int, batch, split: bool | None = None) -> None:
+    """Differential attention of every token over its own sequence's cache: two softmax maps per head (scores
+    q_m . k_m * scale, then softcap * tanh(score / softcap) if softcap > 0) over the keys of the token's chunk of
+    `chunk` positions (0: none), of the last `window` positions (0: all), up to itself; out = (a1 - weight * a2) /
+    sqrt(mean(.^2) + eps) * out_scale * sigmoid(gates[t, gate_at + head]). q float32 [tokens, heads x 2 x dim]; out
+    [tokens, heads x value_dim] in the cache's dtype; `gates` float32 rows (None: no gate). `split`: a block of eight
+    warps per (token, head) instead of a warp (default: for steps of few tokens)."""
+    _cuda(out, q, gates)
+    tokens = batch.n_tokens
+    assert q.dtype == torch.float32 and out.dtype == cache.dtype and cache.head_dim == 2 * dim
+    assert q.shape[1] == heads * 2 * dim and out.shape[1] == heads * cache.value_dim
+    assert gates is None or (gates.dtype == torch.float32 and gates.shape[0] >= tokens)
+    if split is None:
+        split = tokens * heads <= 4 * _multiprocessors()
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    _check(_fn("diff_attention", "dllm_diff_attention")(
+        out.data_ptr(), q.data_ptr(), gate_ptr, gates.shape[1] if gates is not None else 0, cache.base_ptr,
+        cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, dim, cache.value_dim,
+        batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), tokens, float(scale),
+        float(softcap or 0.0), float(weight), float(eps), float(out_scale), int(chunk or 0), int(window or 0),
+        1 if split else 0, _code(cache.dtype), _stream()), "diff_attention",
+        lambda: f"dim={dim}, value_dim={cache.value_dim} (at most 256)")
+
+
+def moe_route(chosen: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor,
+              bias: torch.Tensor | None, top: int) -> None:
+    """Per row of x (float32, or the activations in bfloat16): logits = router x + bias in float32; chosen[t] = the `top` experts with the largest
+    logits, largest first (the lower expert on ties); weights[t] = the softmax over those logits only."""
+    _cuda(chosen, weights, x, router, bias)
+    tokens, width = x.shape
+    experts = router.shape[0]
+    assert router.dtype == torch.float32 and router.shape[1] == width
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == experts)
+    assert chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    assert chosen.numel() >= tokens * top and weights.numel() >= tokens * top
+    _check(_fn("moe", "dllm_moe_route")(x.data_ptr(), width, router.data_ptr(),
+                                        bias.data_ptr() if bias is not None else None, experts, int(top), tokens,
+                                        chosen.data_ptr(), weights.data_ptr(), _code(x.dtype), _stream()), "moe_route",
+           lambda: f"experts={experts} (at most 256), top={top} (at most 16 and at most experts)")
+
+
+def moe_up(act: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, chosen: torch.Tensor, top: int, limit: float,
+           alpha: float, shift: float) -> None:
+    """act[t, k] = glu(W[chosen[t, k]] h[t]) for every token and choice: W [experts, 2 ff, width] interleaves gate and
+    up rows; glu = g sigmoid(alpha g) (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit), in float32."""
+    _cuda(act, h, w_gate_up, chosen)
+    tokens, width = h.shape
+    ff = w_gate_up.shape[1] // 2
+    assert h.dtype == w_gate_up.dtype == act.dtype and w_gate_up.shape[2] == width and chosen.dtype == torch.int32
+    assert act.numel() >= tokens * top * ff and chosen.numel() >= tokens * top
+    _check(_fn("moe", "dllm_moe_up")(act.data_ptr(), h.data_ptr(), width, w_gate_up.data_ptr(), ff, int(top), tokens,
+                                     chosen.data_ptr(), float(limit), float(alpha), float(shift), _code(h.dtype),
+                                     _stream()), "moe_up")
+
+
+def moe_down(out: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+             top: int, accumulate: bool = False) -> None:
+    """out[t] (float32) = sum over k of weights[t, k] * W_down[chosen[t, k]] act[t, k] (added to out if
+    `accumulate`). W_down [experts, width, ff]."""
+    _cuda(out, act, w_down, chosen, weights)
+    tokens, width = out.shape
+    ff = w_down.shape[2]
+    assert out.dtype == torch.float32 and act.dtype == w_down.dtype and w_down.shape[1] == width
+    assert act.numel() >= tokens * top * ff and chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    _check(_fn("moe", "dllm_moe_down")(out.data_ptr(), act.data_ptr(), ff, w_down.data_ptr(), width, int(top), tokens,
+                                       chosen.data_ptr(), weights.data_ptr(), 1 if accumulate else 0,
+                                       _code(act.dtype), _stream()), "moe_down")
 
 
 def concat_restart(both: torch.Tensor, x: torch.Tensor, kept: torch.Tensor, start: torch.Tensor | None) -> None:

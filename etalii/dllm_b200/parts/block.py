@@ -2,9 +2,15 @@
 with them as keyword arguments, exposes them as `parts` (name -> part) and its one mixer as `mixer`, and runs them
 in `forward(x, batch, cache, rt, write_cache)` on the float32 residual stream x.
 
-"pre_norm": x += mixer(norm(x)); x += feed_forward(norm(x)) (reference: src/etalii_dllm/transformer.py:493-558)."""
+"pre_norm": x += mixer(norm(x)); x += feed_forward(norm(x)) (reference: src/etalii_dllm/transformer.py:493-558).
+"output_norm": x += norm(mixer(x)); x += norm(feed_forward(x)): the sublayers read the stream itself and the norm sits
+on what they return."""
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
+from .norm import StreamOperand
 from .registry import register_part
 
 
@@ -49,5 +55,52 @@ class PreNormMixerBlock:
         self.mixer.forward(normed(self.mixer_norm, self.mixer, x, rt), x, batch, cache, rt, write_cache)
 
 
+def stream_input(consumer, x, rt):
+    """The stream as `consumer`'s input: a consumer that says so (`accepts_stream`) gets it still in float32 with
+    the rounding pending, anyone else the rounded activations."""
+    operand = StreamOperand(x, rt)
+    return operand if getattr(consumer, "accepts_stream", False) else operand.tensor()
+
+
+class OutputNormBlock:
+    """x += mixer_norm(mixer(x)); x += feed_forward_norm(feed_forward(x)). Each sublayer writes its float32 output to
+    a work buffer (`epilogue=ops.EPI_STORE_F32`) and the norm adds the normed rows into the stream in one kernel
+    (`add_normed`)."""
+
+    PARTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm) -> None:
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.parts = {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
+                      "feed_forward_norm": feed_forward_norm}
+
+    def forward(self, x, batch, cache, rt, write_cache: bool = True) -> None:
+        out = rt.ws.buffer("sublayer_out", tuple(x.shape), torch.float32)
+        self.mixer.forward(stream_input(self.mixer, x, rt), out, batch, cache, rt, write_cache,
+                           epilogue=ops.EPI_STORE_F32)
+        self.mixer_norm.add_normed(x, out, rt)
+        self.feed_forward.forward(stream_input(self.feed_forward, x, rt), out, batch, rt, epilogue=ops.EPI_STORE_F32)
+        self.feed_forward_norm.add_normed(x, out, rt)
+
+
+class OutputNormMixerBlock:
+    """A layer without a feed-forward: x += mixer_norm(mixer(x))."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    def __init__(self, mixer, mixer_norm) -> None:
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.parts = {"mixer": mixer, "mixer_norm": mixer_norm}
+
+    def forward(self, x, batch, cache, rt, write_cache: bool = True) -> None:
+        out = rt.ws.buffer("sublayer_out", tuple(x.shape), torch.float32)
+        self.mixer.forward(stream_input(self.mixer, x, rt), out, batch, cache, rt, write_cache,
+                           epilogue=ops.EPI_STORE_F32)
+        self.mixer_norm.add_normed(x, out, rt)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "output_norm", OutputNormBlock)
+register_part("block", "output_norm_mixer", OutputNormMixerBlock)
 register_part("block", "pre_norm_mixer", PreNormMixerBlock)

@@ -97,7 +97,8 @@ class ClampedGLU:
         self.w_gate_up = fused.contiguous().to(rt.device)
         self.w_down = rt.to_device(tensors["down"], rt.dtype)
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt) -> None:
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt, epilogue: int = ops.EPI_RESIDUAL) -> None:
+        """Adds into `residual` (float32), or with `epilogue=ops.EPI_STORE_F32` writes it."""
         if isinstance(h, NormedInput):
             h = h.tensor()
         rows = h.shape[0]
@@ -109,7 +110,7 @@ class ClampedGLU:
             both = rt.ws.buffer("ffn_gate_up", (rows, 2 * self.intermediate_size), rt.dtype)
             ops.gemm(both, h, self.w_gate_up, ops.EPI_STORE_T)
             ops.glu_clamped(act, both, self.limit, self.alpha, self.shift)
-        ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
+        ops.gemm(residual, act, self.w_down, epilogue)
 
     def kernel_libraries(self, rt) -> set[str]:
         if rt.dtype != torch.bfloat16:

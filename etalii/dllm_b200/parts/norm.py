@@ -26,6 +26,24 @@ class NormedInput:
         return self._tensor
 
 
+class StreamOperand:
+    """A sublayer's input that is the residual stream itself: `x` float32, and `tensor()` its rounding to the
+    activation type, made once however many products read it."""
+
+    def __init__(self, x: torch.Tensor, rt) -> None:
+        self.x, self.rt, self.shape = x, rt, x.shape
+        self._tensor = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            if self.rt.dtype == torch.float32:
+                self._tensor = self.x
+            else:
+                self._tensor = self.rt.ws.buffer("stream_operand", tuple(self.x.shape), self.rt.dtype)
+                ops.cast_rows(self._tensor, self.x)
+        return self._tensor
+
+
 class RMSNorm:
     def __init__(self, hidden_size: int, eps: float) -> None:
         self.hidden_size, self.eps = int(hidden_size), float(eps)
@@ -63,6 +81,10 @@ class RMSNorm:
 
     def lazy(self, x: torch.Tensor, rt) -> NormedInput:
         return NormedInput(self, x, rt)
+
+    def add_normed(self, residual: torch.Tensor, y: torch.Tensor, rt) -> None:
+        """residual += norm(y): for an arrangement that norms a sublayer's output (y float32 [tokens, hidden])."""
+        ops.norm_add_residual(residual, y, self.weight, self.eps)
 
 
 class LayerNorm:
