@@ -831,6 +831,25 @@ def tisalorn_config(size: dict) -> dict:
             "layers": [kinds[order[i % 3]] for i in range(size["layers"])]}
 
 
+def satavik_config(size: dict) -> dict:
+    """A Satavik model of `size`: differential attention whose two maps have half a head's size each (so queries, keys
+    and values are as wide as the Llama model's), every second layer reading the keys of the layer before it; a
+    mixture of eight experts of a quarter of the feed-forward width, two a token, beside a shared expert of half the
+    width: a token's products are as large as the Llama model's. Chunks of 8,192 positions."""
+    h, g, d = size["heads"], size["kv_heads"], size["dim"]
+    mlp = {"kind": "moe", "expert": {"ff": size["ff"] // 4, "limit": 7.0}, "router": {"experts": 8, "top": 2},
+           "shared": {"ff": size["ff"] // 2, "limit": 7.0}}
+    layers = []
+    for i in range(size["layers"]):
+        mixer = {"heads": h, "kv_heads": g, "dim": d // 2, "vdim": d, "scale": (d // 2) ** -0.5, "softcap": 50.0,
+                 "diff": 0.3, "mask": {"size": 8192}, "rot": {"base": 500000.0, "dims": d // 2}}
+        if i % 2:
+            mixer["kv_from"] = i - 1
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Satavik", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "max_position": 8192, "layers": layers}
+
+
 def llama_config_of(size: dict) -> dict:
     return dict(SMOLLM2_135M, num_hidden_layers=size["layers"], hidden_size=size["width"],
                 num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
@@ -863,10 +882,80 @@ def step_trace(engine, run_step) -> dict:
             for name in sorted(totals, key=lambda n: -totals[n])}
 
 
+def tisalorn_rooflines(row: dict, size: dict, batch: int, peak: dict) -> dict:
+    h, d, b = size["heads"], size["dim"], batch
+    state_bytes = 2 * 4 * b * h * d * d  # a decode step reads and writes every sequence's matrices once
+    scan_fmas = {"decay_scan": 2, "delta_scan": 3}  # multiply-adds per matrix element and token
+    fp32_peak = 148 * 128 * 2 * 1.965e9  # (148 multiprocessors x 128 lanes x 2 flops at the top clock)
+    roofline = {}
+    for name, fmas in scan_fmas.items():
+        decode = row["tisalorn"]["decode_kernels"].get(name)
+        prefill = row["tisalorn"]["prefill_kernels"].get(name)
+        if decode:
+            roofline[name + "_decode_hbm_frac"] = round(state_bytes / (decode["us"] * 1e-6) / 1e9 / peak["hbm_gbs"], 4)
+        if prefill:
+            flops = 2 * fmas * PREFILL_TOKENS * h * d * d
+            roofline[name + "_prefill_fp32_frac"] = round(flops / (prefill["us"] * 1e-6) / fp32_peak, 4)
+    return roofline
+
+
+def _first(kernels: dict, *prefixes: str):
+    """The first kernel of a trace whose name starts with one of `prefixes` (traces are ordered by total time)."""
+    for name, value in kernels.items():
+        if name.startswith(prefixes):
+            return value
+    return None
+
+
+def satavik_rooflines(row: dict, size: dict, batch: int, peak: dict, contexts: list) -> dict:
+    """The new kernels and the Llama kernels that do the like work, each against its own roofline: attention in a
+    decode step against the keys and values it must read at the HBM rate, attention in a prompt step against its
+    multiply-adds at the bf16 tensor rate (causal: half of tokens^2), the experts' products in a decode step against
+    the weights they must read, in a prompt step against their multiply-adds."""
+    h, g, d, width, ff = size["heads"], size["kv_heads"], size["dim"], size["width"], size["ff"]
+    out = {}
+    kv_bytes = 2 * sum(contexts) * g * 2 * d  # keys and values of every sequence's context, bfloat16
+    attention_flops = 2 * 2 * h * d * PREFILL_TOKENS * PREFILL_TOKENS / 2
+    for model, names in (("satavik", ("diff_attention",)), ("llama", ("attention",))):
+        decode = _first(row[model]["decode_kernels"], *names)
+        prefill = _first(row[model]["prefill_kernels"], *names)
+        if decode:
+            out[f"{model}_attention_decode_hbm_frac"] = round(kv_bytes / (decode["us"] * 1e-6) / 1e9 / peak["hbm_gbs"], 4)
+        if prefill:
+            out[f"{model}_attention_prefill_bf16_frac"] = round(
+                attention_flops / (prefill["us"] * 1e-6) / 1e12 / peak["bf16_tflops"], 4)
+    # a decode step of `batch` tokens touches at most min(8, 2 batch) experts' weights (gate, up, down: 3 ff/4 width each)
+    touched = min(8, 2 * batch)
+    expert_bytes = 2 * touched * 3 * (ff // 4) * width
+    expert_flops = 2 * PREFILL_TOKENS * 2 * 3 * (ff // 4) * width
+    for phase, work, unit in (("decode", expert_bytes, "hbm"), ("prefill", expert_flops, "bf16")):
+        kernels = row["satavik"][phase + "_kernels"]
+        us = sum(k["us"] * k["launches"] for name, k in kernels.items() if name.startswith("moe_")) / \
+            max(1, (_first(kernels, "moe_route") or {"launches": 1})["launches"])
+        if us:
+            rate = work / (us * 1e-6)
+            out[f"satavik_experts_{phase}_{unit}_frac"] = round(
+                rate / 1e9 / peak["hbm_gbs"] if unit == "hbm" else rate / 1e12 / peak["bf16_tflops"], 4)
+    # the like kernels of the Llama model: its two feed-forward products
+    dense_bytes, dense_flops = 2 * 3 * ff * width, 2 * PREFILL_TOKENS * 3 * ff * width
+    for phase, work, unit in (("decode", dense_bytes, "hbm"), ("prefill", dense_flops, "bf16")):
+        kernels = row["llama"][phase + "_kernels"]
+        us = sum(k["us"] for name, k in kernels.items() if "swiglu" in name or (name.startswith("gemm residual") and
+                                                                                  f"K={ff}" in name))
+        if us:
+            rate = work / (us * 1e-6)
+            out[f"llama_feed_forward_{phase}_{unit}_frac"] = round(
+                rate / 1e9 / peak["hbm_gbs"] if unit == "hbm" else rate / 1e12 / peak["bf16_tflops"], 4)
+    return out
+
+
+DESIGNS = {"tisalorn": ("Tisalorn", tisalorn_config), "satavik": ("Satavik", satavik_config)}
+
+
 def design_comparison(args) -> int:
-    """`--design tisalorn`: prefill and decode throughput of Tisalorn models at layer sizes like a real model's (random
-    weights) beside a Llama model of the same width, heads, feed-forward and depth; then where the time of a prompt
-    step and of a decode step goes, launch by launch, with the new kernels' distance to their rooflines."""
+    """`--design NAME`: prefill and decode throughput of models of that design at layer sizes like a real model's
+    (random weights) beside a Llama model of the same width, heads, feed-forward and depth; then where the time of a
+    prompt step and of a decode step goes, launch by launch, with the new kernels' distance to their rooflines."""
     import gc
 
     import numpy as np
@@ -878,7 +967,8 @@ def design_comparison(args) -> int:
     from etalii.dllm_b200.engine.engine import Engine
 
     peak = peaks()
-    out = {"design": "Tisalorn", "beside": "llama of equal width, heads, feed-forward and depth", "dtype": "bf16",
+    design = args.design
+    out = {"design": DESIGNS[design][0], "beside": "llama of equal width, heads, feed-forward and depth", "dtype": "bf16",
            "data": "synthetic: seeded random token ids, seeded random weights", "batch": args.batch,
            "prefill_tokens": PREFILL_TOKENS, "peaks": peak["source"], "sizes": {}}
     warmup = max(3, args.warmup)
@@ -886,7 +976,7 @@ def design_comparison(args) -> int:
     for size_name in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
         size = DESIGN_SIZES[size_name]
         row = {"config": size}
-        for model, config_dict in (("tisalorn", tisalorn_config(size)), ("llama", llama_config_of(size))):
+        for model, config_dict in ((design, DESIGNS[design][1](size)), ("llama", llama_config_of(size))):
             config = config_from_dict(config_dict)
             cache_tokens = 64 * (-(-(PREFILL_TOKENS + warmup + steps + 64) // 64)) * max(args.batch, 2)
             engine = Engine.from_random(config, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=cache_tokens,
@@ -894,9 +984,9 @@ def design_comparison(args) -> int:
             vocab = size["vocab"]
             prompts = make_prompts(args.batch, vocab, seed=1)
             if args.profile in ("prefill", "decode"):  # a small case for ncu: a few steps, no JSON
-                if model == "tisalorn" and args.profile == "prefill":
+                if model == design and args.profile == "prefill":
                     print(f"profile prefill ({size_name}): {prefill_run(engine, vocab, warmup=1, repeats=1):.4f} ms")
-                elif model == "tisalorn":
+                elif model == design:
                     ms, launches, _ = decode_run(engine, prompts, 8, 3)
                     print(f"profile decode ({size_name}): {ms / 8:.4f} ms per step, {launches} launches per step")
                 del engine
@@ -936,23 +1026,13 @@ def design_comparison(args) -> int:
         if args.profile in ("prefill", "decode"):
             continue
         # the new kernels against their rooflines
-        h, d, b = size["heads"], size["dim"], args.batch
-        state_bytes = 2 * 4 * b * h * d * d  # a decode step reads and writes every sequence's matrices once
-        scan_fmas = {"decay_scan": 2, "delta_scan": 3}  # multiply-adds per matrix element and token
-        fp32_peak = 148 * 128 * 2 * 1.965e9  # (148 multiprocessors x 128 lanes x 2 flops at the top clock)
-        roofline = {}
-        for name, fmas in scan_fmas.items():
-            decode = row["tisalorn"]["decode_kernels"].get(name)
-            prefill = row["tisalorn"]["prefill_kernels"].get(name)
-            if decode:
-                roofline[name + "_decode_hbm_frac"] = round(state_bytes / (decode["us"] * 1e-6) / 1e9 / peak["hbm_gbs"], 4)
-            if prefill:
-                flops = 2 * fmas * PREFILL_TOKENS * h * d * d
-                roofline[name + "_prefill_fp32_frac"] = round(flops / (prefill["us"] * 1e-6) / fp32_peak, 4)
-        row["roofline"] = roofline
-        row["tisalorn_over_llama"] = {
-            "prefill": round(row["tisalorn"]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"], 3),
-            "decode": round(row["tisalorn"]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"], 3)}
+        if design == "tisalorn":
+            row["roofline"] = tisalorn_rooflines(row, size, args.batch, peak)
+        else:
+            row["roofline"] = satavik_rooflines(row, size, args.batch, peak, [len(p) + 1 for p in prompts])
+        row[design + "_over_llama"] = {
+            "prefill": round(row[design]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"], 3),
+            "decode": round(row[design]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"], 3)}
         out["sizes"][size_name] = row
     if args.profile not in ("prefill", "decode"):
         print(json.dumps(out))
@@ -961,7 +1041,7 @@ def design_comparison(args) -> int:
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--design", choices=("tisalorn",),
+    parser.add_argument("--design", choices=sorted(DESIGNS),
                         help="instead of the benchmark: prefill and decode throughput of this design at layer sizes "
                              "like a real model's, beside a Llama model of equal size, and its kernels' rooflines")
     parser.add_argument("--size", default="", help="with --design: which sizes (comma separated; default all)")

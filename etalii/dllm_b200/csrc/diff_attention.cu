@@ -16,28 +16,13 @@
 // A cache entry holds keys of 2 * dim and values of vdim per position and kv head:
 // [page][ keys: kv_head, row, 2 dim | values: kv_head, row, vdim ].
 #include "common.cuh"
+#include "wide_kv.cuh"
 
 namespace {
 constexpr int WARPS = 4;
 constexpr int SPLIT_WARPS = 8;
 constexpr int MAX_DIM = 256;     // of one map's query or key
 constexpr int MAX_VDIM = 256;
-
-struct WideKv {
-  void* base;
-  const int* page_table;
-  int max_pages, page_size, kv_heads, key_dim, value_dim;
-};
-__device__ __forceinline__ size_t page_elems(const WideKv& c) {
-  return (size_t)c.kv_heads * c.page_size * (size_t)(c.key_dim + c.value_dim);
-}
-__device__ __forceinline__ size_t key_at(const WideKv& c, int page, int g, int row) {
-  return (size_t)page * page_elems(c) + ((size_t)g * c.page_size + row) * c.key_dim;
-}
-__device__ __forceinline__ size_t value_at(const WideKv& c, int page, int g, int row) {
-  return (size_t)page * page_elems(c) + (size_t)c.kv_heads * c.page_size * c.key_dim +
-         ((size_t)g * c.page_size + row) * c.value_dim;
-}
 
 template <typename T> struct Vec;
 template <> struct Vec<float> { static constexpr int N = 4; };
@@ -208,12 +193,6 @@ __device__ __forceinline__ void map_finish(const MapState& st, O* orow, int vdim
     int d = lane + 32 * i;
     if (d < vdim) orow[d] = from_float<O>(o[i] * factor);
   }
-}
-
-__device__ __forceinline__ int first_visible(int pos, int chunk, int window) {
-  int first = chunk > 0 ? (pos / chunk) * chunk : 0;
-  if (window > 0 && pos + 1 - window > first) first = pos + 1 - window;
-  return first;
 }
 
 struct DiffArgs {

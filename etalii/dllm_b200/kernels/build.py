@@ -37,6 +37,7 @@ SOURCES = {
     "attention_decode_static": "attention_decode_static.cu",
     "recurrent": "recurrent.cu",
     "diff_attention": "diff_attention.cu",
+    "diff_attention_prefill": "diff_attention_prefill.cu",
     "moe": "moe.cu",
     "sampling": "sampling.cu",
     "step_launcher": "step_launcher.cu",

@@ -41,6 +41,10 @@ _prototypes = {
                                                 c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                 c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int,
                                                 c_void_p],
+    ("diff_attention_prefill", "dllm_diff_attention_prefill"): [
+        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_int,
+        c_void_p],
     ("moe", "dllm_moe_route"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                 c_void_p],
     ("moe", "dllm_moe_up"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_float,
@@ -336,6 +340,30 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | Non
         float(softcap or 0.0), float(weight), float(eps), float(out_scale), int(chunk or 0), int(window or 0),
         1 if split else 0, _code(cache.dtype), _stream()), "diff_attention",
         lambda: f"dim={dim}, value_dim={cache.value_dim} (at most 256)")
+
+
+def diff_attention_prefill_supported(cache, dim: int) -> bool:
+    return cache.dtype == torch.bfloat16 and cache.page_size == 64 and dim % 8 == 0 and dim <= 128 and \
+        cache.value_dim % 8 == 0 and cache.value_dim <= 128
+
+
+def diff_attention_prefill(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | None, gate_at: int, cache,
+                           heads: int, dim: int, scale: float, softcap: float, weight: float, eps: float,
+                           out_scale: float, chunk: int, window: int, batch) -> None:
+    """`diff_attention` for the new tokens of a prompt-sized step on the tensor cores (bfloat16; dim and value_dim
+    multiples of 8 up to 128; pages of 64): tiles of 64 queries of one sequence and head, a group of warps per map."""
+    _cuda(out, q, gates)
+    assert diff_attention_prefill_supported(cache, dim) and q.dtype == torch.float32 and out.dtype == torch.bfloat16
+    assert q.shape[1] == heads * 2 * dim and out.shape[1] == heads * cache.value_dim and cache.head_dim == 2 * dim
+    assert gates is None or (gates.dtype == torch.float32 and gates.shape[0] >= batch.n_tokens)
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    _check(_fn("diff_attention_prefill", "dllm_diff_attention_prefill")(
+        out.data_ptr(), q.data_ptr(), gate_ptr, gates.shape[1] if gates is not None else 0, cache.base_ptr,
+        cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, dim, cache.value_dim,
+        batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(), batch.cu_seqlens.data_ptr(), batch.start.data_ptr(),
+        batch.slots.data_ptr(), batch.n_tiles, float(scale), float(softcap or 0.0), float(weight), float(eps),
+        float(out_scale), int(chunk or 0), int(window or 0), _stream()), "diff_attention_prefill",
+        lambda: f"dim={dim}, value_dim={cache.value_dim}: multiples of 8 up to 128; pages of 64")
 
 
 def moe_route(chosen: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor,

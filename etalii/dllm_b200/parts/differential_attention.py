@@ -100,14 +100,20 @@ class DifferentialAttention:
         ops.map_prepare(rows, 0, k_at, v_at, q, cache, heads, dim, self.q_weight, self.k_weight, self.eps, table,
                         rotary_dim, batch, writes)
         attended = rt.ws.buffer("attended", (n, heads * vdim), rt.dtype)
-        ops.diff_attention(attended, q, rows, gate_at, cache, heads, dim, self.scale, self.softcap, self.weight,
-                           self.eps, 1.0 - self.diff, self.chunk or 0, self.window or 0, batch)
+        kernel = ops.diff_attention
+        if not batch.is_decode and ops.diff_attention_prefill_supported(cache, dim):
+            kernel = ops.diff_attention_prefill  # (portions of prompts: tiles of 64 queries on the tensor cores)
+        kernel(attended, q, rows, gate_at, cache, heads, dim, self.scale, self.softcap, self.weight, self.eps,
+               1.0 - self.diff, self.chunk or 0, self.window or 0, batch)
         ops.gemm(residual, attended, self.w_o, epilogue)
 
     def kernel_libraries(self, rt) -> set[str]:
         if rt.dtype != torch.bfloat16:
             return {"gemm_simt", "elementwise", "diff_attention"}
-        return {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise", "diff_attention"}
+        names = {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise", "diff_attention"}
+        if self.dim % 8 == 0 and self.vdim % 8 == 0 and self.dim <= 128 and self.vdim <= 128:
+            names.add("diff_attention_prefill")
+        return names
 
 
 register_part("mixer", "differential_attention", DifferentialAttention)

@@ -15,6 +15,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DTYPES = [("float32", torch.float32), ("bfloat16", torch.bfloat16)]
 PART_TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+SHARP_TOL = {torch.float32: 2e-5, torch.bfloat16: 5e-2}
+"""For the tests whose weights make one score stand out: such sharp maps amplify the rounding of bfloat16 keys, and what
+the tests decide (a key seen or not) moves the output by more than 0.2."""
 
 
 def _runtime(dtype, max_length=1024):
@@ -279,7 +282,7 @@ def test_a_key_at_the_edge_of_a_chunk_counts_only_from_inside(name, dtype, chunk
     for row in (start + 1, n - 1, n):  # in the prompt, and the token decoded alone
         sees = back == 0
         assert (rel_error(want[row], other[row]) > 0.2) == sees  # the test's premise
-        assert rel_error(got[row], want[row]) <= PART_TOL[dtype]
+        assert rel_error(got[row], want[row]) <= SHARP_TOL[dtype]
 
 
 @pytest.mark.parametrize("name,dtype", DTYPES)
@@ -315,7 +318,7 @@ def test_a_far_key_among_hundreds(name, dtype, far):
     other = _plain_mixer(weights, p, without)
     for row in (n - 1, n):
         assert rel_error(want[row], other[row]) > 0.2  # the test's premise: that key matters
-        assert rel_error(got[row], want[row]) <= PART_TOL[dtype]
+        assert rel_error(got[row], want[row]) <= SHARP_TOL[dtype]
 
 
 @pytest.mark.parametrize("name,dtype", DTYPES)
