@@ -20,7 +20,7 @@
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int SPLIT_WARPS = 8;
+constexpr int SPLIT_WARPS = 16;
 constexpr int MAX_DIM = 256;     // of one map's query or key
 constexpr int MAX_VDIM = 256;
 
@@ -158,7 +158,7 @@ __device__ __forceinline__ void map_tile(MapState& st, const float* q_s, const W
     st.m[m] = m_new;
   }
   int count = min(32, end - j0);
-  for (int jj = 0; jj < count; ++jj) {
+  auto one_value_row = [&](int jj) {
     float p0 = __shfl_sync(0xffffffffu, p[0], jj), p1 = __shfl_sync(0xffffffffu, p[1], jj);
     int pg = __shfl_sync(0xffffffffu, page, jj);
     const T* vrow = base + value_at(cache, pg, g, (j0 + jj) % ps);
@@ -171,6 +171,12 @@ __device__ __forceinline__ void map_tile(MapState& st, const float* q_s, const W
         st.acc[1][i] = fmaf(p1, v, st.acc[1][i]);
       }
     }
+  };
+  if (count == 32) {  // a whole tile: eight rows' loads on their way at a time
+#pragma unroll 8
+    for (int jj = 0; jj < 32; ++jj) one_value_row(jj);
+  } else {
+    for (int jj = 0; jj < count; ++jj) one_value_row(jj);
   }
 }
 
@@ -328,7 +334,7 @@ DLLM_EXPORT int dllm_map_prepare(const float* rows, int ld, int q_at, int k_at, 
   return DLLM_BAD_ARGUMENT;
 }
 
-// `split` != 0: a block of eight warps per (token, head) instead of a warp.
+// `split` != 0: a block of sixteen warps per (token, head) instead of a warp.
 DLLM_EXPORT int dllm_diff_attention(void* out, const float* q, const float* gates, int gate_ld, void* cache_base,
                                     const int* page_table, int max_pages, int page_size, int heads, int kv_heads, int dim,
                                     int vdim, const int* tok_seq, const int* tok_pos, const int* slots, int tokens,

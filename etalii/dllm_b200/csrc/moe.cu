@@ -1,7 +1,7 @@
 // A mixture of gated feed-forward experts, token by token: every token goes to the `top` experts with the largest router
 // logits, weighted by the softmax over those logits only.
 //
-//   moe_route:  a warp per token: logits = W_r x + b in float32 from the float32 stream, `top` rounds of arg-max (the
+//   moe_route:  a block per token: logits = W_r x + b in float32 from the float32 stream, `top` rounds of arg-max (the
 //               lower expert on ties), then the weights.
 //   moe_up:     per (token, choice): the chosen expert's gate and up rows times the token's activations, then the
 //               clamped gated unit g sigmoid(alpha g) (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit).
@@ -67,25 +67,26 @@ template <typename X>
 __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(
     const X* __restrict__ x, int width, const float* __restrict__ w, const float* __restrict__ bias, int experts,
     int top, int tokens, int* __restrict__ chosen, float* __restrict__ weights) {
-  __shared__ float logits[WARPS][MAX_EXPERTS];
+  // a block per token: its warps share the experts' logits out, warp 0 then chooses
+  __shared__ float logits[MAX_EXPERTS];
   pdl_launch_dependents();
   pdl_wait();
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int t = blockIdx.x * WARPS + warp;
-  if (t >= tokens) return;
+  int t = blockIdx.x;
   const X* row = x + (size_t)t * width;
-  for (int e = 0; e < experts; ++e) {
+  for (int e = warp; e < experts; e += WARPS) {
     float s = warp_sum(lane_dot_router(w + (size_t)e * width, row, width, lane));
-    if (lane == 0) logits[warp][e] = s + (bias != nullptr ? bias[e] : 0.f);
+    if (lane == 0) logits[e] = s + (bias != nullptr ? bias[e] : 0.f);
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float kept[MAX_TOP];
   float largest = 0.f, total = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int where = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
-      float v = logits[warp][e];
+      float v = logits[e];
       if (v > best) { best = v; where = e; }  // (ascending e: the first of equals stays)
     }
 #pragma unroll
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(
     total += kept[k];
     if (lane == 0) {
       chosen[(size_t)t * top + k] = where;
-      logits[warp][where] = -INFINITY;
+      logits[where] = -INFINITY;
     }
     __syncwarp();
   }
@@ -160,7 +161,7 @@ DLLM_EXPORT int dllm_moe_route(const void* x, int width, const float* w, const f
   if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > MAX_TOP || top > experts || width <= 0)
     return DLLM_UNSUPPORTED_SIZE;
   if (x == nullptr || w == nullptr || chosen == nullptr || weights == nullptr) return DLLM_BAD_ARGUMENT;
-  dim3 grid((tokens + WARPS - 1) / WARPS), block(WARPS * 32);
+  dim3 grid(tokens), block(WARPS * 32);
   if (dtype == DLLM_F32)
     return dllm_launch_pdl(moe_route_kernel<float>, grid, block, 0, stream, (const float*)x, width, w, bias, experts,
                            top, tokens, chosen, weights);

@@ -51,6 +51,12 @@ _prototypes = {
                              c_float, c_int, c_void_p],
     ("moe", "dllm_moe_down"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                c_int, c_void_p],
+    ("moe_grouped", "dllm_moe_sort"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("moe_grouped", "dllm_moe_grouped_up"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                             c_void_p, c_float, c_float, c_float, c_void_p],
+    ("moe_grouped", "dllm_moe_grouped_down"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_void_p, c_void_p, c_void_p],
+    ("moe_grouped", "dllm_moe_combine"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("elementwise", "dllm_concat_restart"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "dllm_decay_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
@@ -323,7 +329,7 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | Non
     q_m . k_m * scale, then softcap * tanh(score / softcap) if softcap > 0) over the keys of the token's chunk of
     `chunk` positions (0: none), of the last `window` positions (0: all), up to itself; out = (a1 - weight * a2) /
     sqrt(mean(.^2) + eps) * out_scale * sigmoid(gates[t, gate_at + head]). q float32 [tokens, heads x 2 x dim]; out
-    [tokens, heads x value_dim] in the cache's dtype; `gates` float32 rows (None: no gate). `split`: a block of eight
+    [tokens, heads x value_dim] in the cache's dtype; `gates` float32 rows (None: no gate). `split`: a block of sixteen
     warps per (token, head) instead of a warp (default: for steps of few tokens)."""
     _cuda(out, q, gates)
     tokens = batch.n_tokens
@@ -409,6 +415,49 @@ def moe_down(out: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, chosen:
     _check(_fn("moe", "dllm_moe_down")(out.data_ptr(), act.data_ptr(), ff, w_down.data_ptr(), width, int(top), tokens,
                                        chosen.data_ptr(), weights.data_ptr(), 1 if accumulate else 0,
                                        _code(act.dtype), _stream()), "moe_down")
+
+
+MOE_GROUPED_FROM = 64
+"""Steps of more tokens than this run the experts as grouped tile products (`moe_experts_grouped`); smaller ones read
+each chosen expert's rows once per token (`moe_up`, `moe_down`), which is what few tokens need."""
+
+
+def moe_grouped_supported(tokens: int, dtype, width: int, ff: int) -> bool:
+    return dtype == torch.bfloat16 and tokens > MOE_GROUPED_FROM and width % 8 == 0 and ff % 8 == 0
+
+
+def moe_experts_grouped(out: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                        chosen: torch.Tensor, weights: torch.Tensor, top: int, limit: float, alpha: float, shift: float,
+                        offsets: torch.Tensor, place_pair: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
+                        accumulate: bool = False) -> None:
+    """What `moe_up` and `moe_down` compute, for many tokens (bfloat16): the (token, choice) pairs are put in expert
+    order on the device, every expert's rows run as tile products on the tensor cores (gate/up with the gated unit in
+    the epilogue, then down, scattered back by pair), and a last kernel forms each token's weighted sum. Four launches
+    whose shapes depend on the sizes only. Scratch: offsets [experts + 1] and place_pair [pairs] int32, act [pairs, ff]
+    bfloat16, y [pairs, width] float32."""
+    _cuda(out, h, w_gate_up, w_down, chosen, weights, offsets, place_pair, act, y)
+    tokens, width = h.shape
+    experts, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    pairs = tokens * top
+    assert h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+    assert tuple(w_down.shape) == (experts, width, ff) and w_gate_up.shape[2] == width
+    assert out.dtype == torch.float32 and tuple(out.shape) == (tokens, width)
+    assert offsets.dtype == torch.int32 and offsets.numel() >= experts + 1 and place_pair.numel() >= pairs
+    assert act.dtype == torch.bfloat16 and act.numel() >= pairs * ff and y.dtype == torch.float32
+    assert y.numel() >= pairs * width and chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    stream = _stream()
+    _check(_fn("moe_grouped", "dllm_moe_sort")(chosen.data_ptr(), pairs, experts, offsets.data_ptr(),
+                                               place_pair.data_ptr(), stream), "moe_sort",
+           lambda: f"experts={experts} (at most 256)")
+    _check(_fn("moe_grouped", "dllm_moe_grouped_up")(
+        act.data_ptr(), h.data_ptr(), width, w_gate_up.data_ptr(), ff, experts, int(top), tokens, offsets.data_ptr(),
+        place_pair.data_ptr(), float(limit), float(alpha), float(shift), stream), "moe_grouped_up",
+        lambda: f"width={width} (a multiple of 8)")
+    _check(_fn("moe_grouped", "dllm_moe_grouped_down")(
+        y.data_ptr(), act.data_ptr(), ff, w_down.data_ptr(), width, experts, int(top), tokens, offsets.data_ptr(),
+        place_pair.data_ptr(), stream), "moe_grouped_down", lambda: f"ff={ff} (a multiple of 8)")
+    _check(_fn("moe_grouped", "dllm_moe_combine")(out.data_ptr(), y.data_ptr(), weights.data_ptr(), width, int(top),
+                                                  tokens, 1 if accumulate else 0, stream), "moe_combine")
 
 
 def concat_restart(both: torch.Tensor, x: torch.Tensor, kept: torch.Tensor, start: torch.Tensor | None) -> None:

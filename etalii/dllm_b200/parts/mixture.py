@@ -82,13 +82,24 @@ class ClampedGLUExperts:
         weights = rt.ws.buffer("experts_weights", (n, self.top), torch.float32)
         ops.moe_route(chosen, weights, routed, self.router, self.bias, self.top)
         act = rt.ws.buffer("experts_act", (n * self.top, self.intermediate_size), rt.dtype)
-        ops.moe_up(act, h, self.w_gate_up, chosen, self.top, self.limit, self.alpha, self.shift)
-        ops.moe_down(residual, act, self.w_down, chosen, weights, self.top, accumulate=epilogue == ops.EPI_RESIDUAL)
+        adds = epilogue == ops.EPI_RESIDUAL
+        if ops.moe_grouped_supported(n, rt.dtype, self.hidden_size, self.intermediate_size):
+            # many tokens: the pairs in expert order, every expert's rows as tile products
+            offsets = rt.ws.buffer("experts_offsets", (self.experts + 1,), torch.int32)
+            places = rt.ws.buffer("experts_places", (n * self.top,), torch.int32)
+            pairs_out = rt.ws.buffer("experts_out", (n * self.top, self.hidden_size), torch.float32)
+            ops.moe_experts_grouped(residual, h, self.w_gate_up, self.w_down, chosen, weights, self.top, self.limit,
+                                    self.alpha, self.shift, offsets, places, act, pairs_out, accumulate=adds)
+        else:
+            ops.moe_up(act, h, self.w_gate_up, chosen, self.top, self.limit, self.alpha, self.shift)
+            ops.moe_down(residual, act, self.w_down, chosen, weights, self.top, accumulate=adds)
         if self.shared is not None:
             self.shared.forward(h, residual, batch, rt)  # (adds)
 
     def kernel_libraries(self, rt) -> set[str]:
         names = {"moe", "elementwise"}
+        if rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0:
+            names.add("moe_grouped")
         if self.shared is not None and hasattr(self.shared, "kernel_libraries"):
             names |= set(self.shared.kernel_libraries(rt))
         return names

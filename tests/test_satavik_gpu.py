@@ -96,8 +96,8 @@ def test_router_ties_go_to_the_lower_expert_and_the_bias_decides():
 
 
 @pytest.mark.parametrize("name,dtype", DTYPES)
-@pytest.mark.parametrize("rows", [1, 5, 70])
-@pytest.mark.parametrize("experts,top,ff,shared", [(5, 3, 24, 40), (3, 1, 20, 0), (2, 2, 8, 8)])
+@pytest.mark.parametrize("rows", [1, 5, 70, 333])
+@pytest.mark.parametrize("experts,top,ff,shared", [(5, 3, 24, 40), (3, 1, 20, 0), (2, 2, 8, 8), (40, 2, 136, 0)])
 def test_mixture_part(name, dtype, rows, experts, top, ff, shared):
     from etalii.dllm_b200.kernels import ops
     from etalii.dllm_b200.parts import PartSpec, build_part
