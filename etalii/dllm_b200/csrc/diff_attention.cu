@@ -45,12 +45,40 @@ __device__ __forceinline__ float dot_piece(const float* q, const __nv_bfloat16* 
   return s;
 }
 
-// q (shared memory, float32) . k (cache row); 16-byte pieces where the size allows, one value at a time otherwise.
+__device__ __forceinline__ float4 load_piece(const float* k) { return *(const float4*)k; }
+__device__ __forceinline__ uint4 load_piece(const __nv_bfloat16* k) { return *(const uint4*)k; }
+__device__ __forceinline__ float dot_loaded(const float* q, float4 v) {
+  return fmaf(q[3], v.w, fmaf(q[2], v.z, fmaf(q[1], v.y, q[0] * v.x)));
+}
+__device__ __forceinline__ float dot_loaded(const float* q, uint4 raw) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 x = __bfloat1622float2(p[i]);
+    s = fmaf(q[2 * i], x.x, s);
+    s = fmaf(q[2 * i + 1], x.y, s);
+  }
+  return s;
+}
+
+// q (shared memory, float32) . k (cache row); 16-byte pieces where the size allows (four of them asked for before the
+// first is used: a lane's row is its own, so nothing else hides the loads' latency), one value at a time otherwise.
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* q, const T* k, int n, bool pieces) {
+  constexpr int N = Vec<T>::N;
   float s = 0.f;
   if (pieces) {
-    for (int d = 0; d < n; d += Vec<T>::N) s += dot_piece(q + d, k + d);
+    int d = 0;
+    for (; d + 4 * N <= n; d += 4 * N) {
+      auto v0 = load_piece(k + d), v1 = load_piece(k + d + N), v2 = load_piece(k + d + 2 * N),
+           v3 = load_piece(k + d + 3 * N);
+      s += dot_loaded(q + d, v0);
+      s += dot_loaded(q + d + N, v1);
+      s += dot_loaded(q + d + 2 * N, v2);
+      s += dot_loaded(q + d + 3 * N, v3);
+    }
+    for (; d < n; d += N) s += dot_piece(q + d, k + d);
   } else {
     for (int d = 0; d < n; ++d) s = fmaf(q[d], to_float(k[d]), s);
   }

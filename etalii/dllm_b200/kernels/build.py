@@ -38,6 +38,7 @@ SOURCES = {
     "recurrent": "recurrent.cu",
     "diff_attention": "diff_attention.cu",
     "diff_attention_prefill": "diff_attention_prefill.cu",
+    "diff_attention_decode": "diff_attention_decode.cu",
     "moe": "moe.cu",
     "moe_grouped": "moe_grouped.cu",
     "sampling": "sampling.cu",

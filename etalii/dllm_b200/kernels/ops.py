@@ -45,6 +45,11 @@ _prototypes = {
         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_int,
         c_void_p],
+    ("diff_attention_decode", "dllm_diff_attention_decode_fits"): [c_int, c_int, c_int, c_int, c_int],
+    ("diff_attention_decode", "dllm_diff_attention_decode"): [
+        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+        c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
+        c_void_p],
     ("moe", "dllm_moe_route"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                 c_void_p],
     ("moe", "dllm_moe_up"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_float,
@@ -346,6 +351,59 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | Non
         float(softcap or 0.0), float(weight), float(eps), float(out_scale), int(chunk or 0), int(window or 0),
         1 if split else 0, _code(cache.dtype), _stream()), "diff_attention",
         lambda: f"dim={dim}, value_dim={cache.value_dim} (at most 256)")
+
+
+def diff_attention_decode_supported(cache, heads: int, dim: int) -> bool:
+    """Whether the kernel that serves a token's whole group of query heads per block takes these sizes (bfloat16, at
+    most 8 query heads per kv head, dim and value_dim multiples of 8, two pages of keys and values in shared memory)."""
+    if cache.dtype != torch.bfloat16 or heads % cache.kv_heads or heads // cache.kv_heads > 8:
+        return False
+    if dim % 8 or cache.value_dim % 8 or cache.value_dim > 256 or cache.page_size != 64:
+        return False
+    group = heads // cache.kv_heads
+    padded = next(n for n in (2, 4, 8, 16) if 2 * group <= n)
+    parts = 1
+    while parts < 8 and parts * 2 * cache.value_dim <= 256:
+        parts *= 2
+    floats = group * 2 * dim + padded * 64 + 4 * padded + 64
+    stages = 2 * 64 * (2 * dim + 8 + cache.value_dim) * 2
+    return 4 * floats + max(stages, 4 * parts * padded * cache.value_dim) <= 200 * 1024
+
+
+def diff_attention_decode_splits(tokens: int, kv_heads: int, longest: int) -> int:
+    """Into how many stretches a token's keys are cut: enough blocks (tokens x kv heads x stretches) for two a
+    multiprocessor, at most 16 and at most one per page of the longest context."""
+    wanted = max(1, (2 * _multiprocessors()) // max(1, tokens * kv_heads))
+    return max(1, min(16, wanted, -(-int(longest) // 64)))
+
+
+def diff_attention_decode(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | None, gate_at: int, cache,
+                          heads: int, dim: int, scale: float, softcap: float, weight: float, eps: float,
+                          out_scale: float, chunk: int, window: int, batch, splits: int, partial: torch.Tensor | None,
+                          tickets: torch.Tensor | None) -> None:
+    """`diff_attention` for a step of single tokens (bfloat16): a block per (token, kv head, stretch of keys) serves all
+    query heads of the group from pages staged in shared memory; with `splits` > 1 the last block of a token combines
+    the stretches through `partial` (tokens x kv_heads x splits x 2 group x (value_dim + 2) floats) and `tickets`
+    (tokens x kv_heads int32 zeros, left zero)."""
+    _cuda(out, q, gates, partial, tickets)
+    tokens = batch.n_tokens
+    assert diff_attention_decode_supported(cache, heads, dim) and batch.n_tokens == batch.n_seqs
+    assert q.dtype == torch.float32 and out.dtype == torch.bfloat16 and cache.head_dim == 2 * dim
+    assert q.shape[1] == heads * 2 * dim and out.shape[1] == heads * cache.value_dim
+    group = heads // cache.kv_heads
+    if splits > 1:
+        assert partial.dtype == torch.float32 and tickets.dtype == torch.int32
+        assert partial.numel() >= tokens * cache.kv_heads * splits * 2 * group * (cache.value_dim + 2)
+        assert tickets.numel() >= tokens * cache.kv_heads
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    _check(_fn("diff_attention_decode", "dllm_diff_attention_decode")(
+        out.data_ptr(), q.data_ptr(), gate_ptr, gates.shape[1] if gates is not None else 0, cache.base_ptr,
+        cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, dim, cache.value_dim,
+        batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), tokens, float(scale),
+        float(softcap or 0.0), float(weight), float(eps), float(out_scale), int(chunk or 0), int(window or 0),
+        int(splits), partial.data_ptr() if partial is not None else None,
+        tickets.data_ptr() if tickets is not None else None, _stream()), "diff_attention_decode",
+        lambda: f"dim={dim}, value_dim={cache.value_dim}, {group} query heads per kv head")
 
 
 def diff_attention_prefill_supported(cache, dim: int) -> bool:

@@ -100,11 +100,23 @@ class DifferentialAttention:
         ops.map_prepare(rows, 0, k_at, v_at, q, cache, heads, dim, self.q_weight, self.k_weight, self.eps, table,
                         rotary_dim, batch, writes)
         attended = rt.ws.buffer("attended", (n, heads * vdim), rt.dtype)
-        kernel = ops.diff_attention
-        if not batch.is_decode and ops.diff_attention_prefill_supported(cache, dim):
-            kernel = ops.diff_attention_prefill  # (portions of prompts: tiles of 64 queries on the tensor cores)
-        kernel(attended, q, rows, gate_at, cache, heads, dim, self.scale, self.softcap, self.weight, self.eps,
-               1.0 - self.diff, self.chunk or 0, self.window or 0, batch)
+        common = (self.scale, self.softcap, self.weight, self.eps, 1.0 - self.diff, self.chunk or 0, self.window or 0,
+                  batch)
+        if batch.is_decode and ops.diff_attention_decode_supported(cache, heads, dim):
+            # single tokens: a block per (token, kv head, stretch of keys) serves the whole group of query heads
+            longest = min(batch.max_context, self.chunk or batch.max_context, self.window or batch.max_context)
+            splits = ops.diff_attention_decode_splits(n, kv_heads, longest)
+            partial = tickets = None
+            if splits > 1:
+                partial = rt.ws.buffer("map_partial", (n * kv_heads * splits * 2 * (heads // kv_heads) * (vdim + 2),),
+                                       torch.float32)
+                tickets = rt.ws.zeros("map_tickets", n * kv_heads, torch.int32)
+            ops.diff_attention_decode(attended, q, rows, gate_at, cache, heads, dim, *common, splits, partial, tickets)
+        elif not batch.is_decode and ops.diff_attention_prefill_supported(cache, dim):
+            # portions of prompts: tiles of 64 queries on the tensor cores
+            ops.diff_attention_prefill(attended, q, rows, gate_at, cache, heads, dim, *common)
+        else:
+            ops.diff_attention(attended, q, rows, gate_at, cache, heads, dim, *common)
         ops.gemm(residual, attended, self.w_o, epilogue)
 
     def kernel_libraries(self, rt) -> set[str]:
@@ -112,7 +124,7 @@ class DifferentialAttention:
             return {"gemm_simt", "elementwise", "diff_attention"}
         names = {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise", "diff_attention"}
         if self.dim % 8 == 0 and self.vdim % 8 == 0 and self.dim <= 128 and self.vdim <= 128:
-            names.add("diff_attention_prefill")
+            names |= {"diff_attention_prefill", "diff_attention_decode"}
         return names
 
 
