@@ -1,8 +1,8 @@
 // Differential attention of steps of single tokens (bfloat16 cache). A block serves one token and one kv head, that is
 // ALL query heads of the group and both of their score maps (an "item" is a (head, map) pair), over one stretch of the
 // keys the token sees; `splits` blocks share a token's keys, and the block that finishes last combines their partial
-// results in stretch order (a ticket counter: nobody waits). Keys and values come page by page (64 positions) into two
-// shared-memory stages by cp.async, so a page's latency is paid once, under the work on the page before it:
+// results in stretch order (a ticket counter: nobody waits). Keys and values come page by page (64 positions) into three
+// shared-memory stages by cp.async (two pages on their way while one is worked on), so a page's latency is paid once:
 //
 //   scores:   a thread per (head, key): both maps' q . k from shared memory, scale, cap * tanh(score / cap), masks
 //   softmax:  a warp per item: the page's maximum, the running maximum and sum, the weights in place of the scores
@@ -16,7 +16,7 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int THREADS = 256, WARPS = 8, PAGE = 64, MAX_ITEMS = 16;
+constexpr int THREADS = 256, WARPS = 8, PAGE = 64, MAX_ITEMS = 16, STAGES = 3;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
   float* state_s = s_s + ITEMS * PAGE;                              // m[ITEMS], l[ITEMS], corr[ITEMS], (unused)
   float* red_s = state_s + 4 * ITEMS;                               // [WARPS][MAX_ITEMS / 2] sums of squares (the state
                                                                     // takes four rows: what follows starts on 16 bytes)
-  bf16* k_s = reinterpret_cast<bf16*>(red_s + WARPS * (MAX_ITEMS / 2));  // [2][PAGE][ldk]
-  bf16* v_s = k_s + 2 * PAGE * ldk;                                 // [2][PAGE][vdim]
+  bf16* k_s = reinterpret_cast<bf16*>(red_s + WARPS * (MAX_ITEMS / 2));  // [STAGES][PAGE][ldk]
+  bf16* v_s = k_s + STAGES * PAGE * ldk;                            // [STAGES][PAGE][vdim]
   pdl_launch_dependents();
   pdl_wait();
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -95,8 +95,11 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
     }
     for (int i = tid; i < PAGE * v_pieces; i += THREADS) cp_async_16(v_s + (size_t)stage * PAGE * vdim + i * 8, vsrc + i * 8);
   };
-  if (p_begin < p_end) load_page(0, p_begin);
-  cp_async_commit();
+#pragma unroll
+  for (int ahead = 0; ahead < STAGES - 1; ++ahead) {  // two pages on their way before the first is used
+    if (p_begin + ahead < p_end) load_page(ahead, p_begin + ahead);
+    cp_async_commit();
+  }
 
   // the value phase: parts of the page side by side where the block has more threads than value places
   int parts = 1;
@@ -110,11 +113,11 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
   __syncthreads();
 
   for (int p = p_begin; p < p_end; ++p) {
-    int stage = (p - p_begin) & 1;
-    if (p + 1 < p_end) load_page(stage ^ 1, p + 1);
+    int stage = (p - p_begin) % STAGES;
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();  // this page has landed, and everyone is done with the stage the next load overwrites
+    if (p + STAGES - 1 < p_end) load_page((stage + STAGES - 1) % STAGES, p + STAGES - 1);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
     // scores
     for (int idx = tid; idx < group * PAGE; idx += THREADS) {
       int head = idx / PAGE, key = idx % PAGE;
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
         }
       }
     }
-    __syncthreads();  // the stage and the weights are free
+    __syncthreads();  // the weights' place is free for the next page's scores
   }
   cp_async_wait<0>();
   // the parts' sums meet in the threads of part 0 (through the key/value space, free now)
@@ -213,13 +216,25 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
     if (!last) return;
     __threadfence();
     const float* all = a.partial + ((size_t)t * cache.kv_heads + g) * a.splits * items * stride;
+    // every (item, stretch)'s maximum and sum with one thread each, then each stretch's factor, then the sums: the
+    // loads of a phase do not wait for one another
+    float* m_all = meet;                       // [items][splits] (the key/value space again)
+    float* l_all = m_all + MAX_ITEMS * 16;
+    float* f_all = l_all + MAX_ITEMS * 16;
+    if (tid < items * a.splits) {
+      int it = tid / a.splits, s = tid % a.splits;
+      m_all[tid] = __ldcg(all + ((size_t)s * items + it) * stride + vdim);
+      l_all[tid] = __ldcg(all + ((size_t)s * items + it) * stride + vdim + 1);
+    }
+    __syncthreads();
     if (tid < items) {
-      float best = -INFINITY;
-      for (int s = 0; s < a.splits; ++s) best = fmaxf(best, __ldcg(all + ((size_t)s * items + tid) * stride + vdim));
-      float sum = 0.f;
+      float best = -INFINITY, sum = 0.f;
+      for (int s = 0; s < a.splits; ++s) best = fmaxf(best, m_all[tid * a.splits + s]);
       for (int s = 0; s < a.splits; ++s) {
-        float m = __ldcg(all + ((size_t)s * items + tid) * stride + vdim);
-        if (m != -INFINITY) sum = fmaf(__ldcg(all + ((size_t)s * items + tid) * stride + vdim + 1), expf(m - best), sum);
+        float m = m_all[tid * a.splits + s];
+        float f = m == -INFINITY ? 0.f : expf(m - best);
+        f_all[tid * a.splits + s] = f;
+        sum = fmaf(l_all[tid * a.splits + s], f, sum);
       }
       state_s[tid] = best;
       state_s[ITEMS + tid] = sum;
@@ -229,11 +244,10 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
 #pragma unroll
       for (int it = 0; it < ITEMS; ++it) {
         if (it < items) {
-          float best = state_s[it], sum = 0.f;
-          for (int s = 0; s < a.splits; ++s) {
-            float m = __ldcg(all + ((size_t)s * items + it) * stride + vdim);
-            if (m != -INFINITY) sum = fmaf(__ldcg(all + ((size_t)s * items + it) * stride + d), expf(m - best), sum);
-          }
+          float sum = 0.f;
+#pragma unroll 4
+          for (int s = 0; s < a.splits; ++s)
+            sum = fmaf(__ldcg(all + ((size_t)s * items + it) * stride + d), f_all[it * a.splits + s], sum);
           acc[it] = sum;
         }
       }
@@ -264,7 +278,7 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
 
 size_t shared_bytes(int group, int dim, int vdim, int items_padded) {
   size_t floats = (size_t)group * 2 * dim + (size_t)items_padded * PAGE + 4 * items_padded + WARPS * (MAX_ITEMS / 2);
-  size_t stages = 2 * (size_t)PAGE * (2 * dim + 8 + vdim) * sizeof(bf16);
+  size_t stages = STAGES * (size_t)PAGE * (2 * dim + 8 + vdim) * sizeof(bf16);
   int parts = 1;
   while (parts < 8 && parts * 2 * vdim <= THREADS) parts *= 2;
   size_t meet = (size_t)parts * items_padded * vdim * sizeof(float);  // (shares the stages' space)
@@ -306,7 +320,7 @@ DLLM_EXPORT int dllm_diff_attention_decode(void* out, const float* q, const floa
   if (tokens <= 0) return DLLM_OK;
   int fits = dllm_diff_attention_decode_fits(heads, kv_heads, dim, vdim, page_size);
   if (fits != DLLM_OK) return fits;
-  if (splits < 1 || chunk < 0 || window < 0 || (splits > 1 && (partial == nullptr || tickets == nullptr)))
+  if (splits < 1 || splits > 16 || chunk < 0 || window < 0 || (splits > 1 && (partial == nullptr || tickets == nullptr)))
     return DLLM_BAD_ARGUMENT;
   WideKv cache{cache_base, page_table, max_pages, page_size, kv_heads, 2 * dim, vdim};
   DecodeArgs a{q, gates, gate_ld, tok_seq, tok_pos, slots, heads, dim, scale, softcap, lambda, eps, out_scale,

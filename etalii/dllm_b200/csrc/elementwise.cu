@@ -569,9 +569,11 @@ DLLM_EXPORT int dllm_norm_sum_residual(float* residual, const float* a, const fl
 
 // ---- one RMS-normed sublayer output into the residual -------------------------------------------------------------
 // residual[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w, everything float32; one block per row. The arrangement that
-// norms a sublayer's output instead of its input ends both of its sublayers with this.
+// norms a sublayer's output instead of its input ends both of its sublayers with this. With `copy`, the new rows are
+// also written there as bfloat16: they are the next sublayer's operand, which then needs no kernel to round them.
 __global__ void norm_add_residual_kernel(float* __restrict__ residual, const float* __restrict__ y,
-                                         const float* __restrict__ w, int hidden, float eps) {
+                                         const float* __restrict__ w, __nv_bfloat16* __restrict__ copy, int hidden,
+                                         float eps) {
   __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -582,15 +584,20 @@ __global__ void norm_add_residual_kernel(float* __restrict__ residual, const flo
     s = fmaf(v, v, s);
   }
   float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) residual[base + i] += y[base + i] * inv * w[i];
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = residual[base + i] + y[base + i] * inv * w[i];
+    residual[base + i] = v;
+    if (copy != nullptr) copy[base + i] = __float2bfloat16_rn(v);
+  }
 }
 
-DLLM_EXPORT int dllm_norm_add_residual(float* residual, const float* y, const float* w, int rows, int hidden, float eps,
-                                       cudaStream_t stream) {
+DLLM_EXPORT int dllm_norm_add_residual(float* residual, const float* y, const float* w, void* copy, int rows, int hidden,
+                                       float eps, cudaStream_t stream) {
   if (rows <= 0) return DLLM_OK;
   if (hidden <= 0 || residual == nullptr || y == nullptr || w == nullptr) return DLLM_BAD_ARGUMENT;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  return dllm_launch_pdl(norm_add_residual_kernel, dim3(rows), dim3(threads), 0, stream, residual, y, w, hidden, eps);
+  return dllm_launch_pdl(norm_add_residual_kernel, dim3(rows), dim3(threads), 0, stream, residual, y, w,
+                         (__nv_bfloat16*)copy, hidden, eps);
 }
 
 // ---- the float32 stream as an operand: out = bfloat16(x) ----------------------------------------------------------

@@ -64,6 +64,9 @@ class Runtime:
         self.ws = Workspace(self.device)
         self._device_copies: dict[tuple[int, torch.dtype], torch.Tensor] = {}
         self._shared: dict = {}
+        self.stream_rounded = None
+        """(address, shape, launch count, copy): the residual stream's rounding to the activation type where the kernel
+        that last wrote the stream left one; valid only while no other kernel has been launched since."""
         self._keep: list = []
 
     def to_device(self, tensor: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:

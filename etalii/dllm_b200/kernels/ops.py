@@ -32,7 +32,7 @@ _prototypes = {
     ("elementwise", "dllm_glu_clamped"): [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
     ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                                 c_float, c_void_p],
-    ("elementwise", "dllm_norm_add_residual"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    ("elementwise", "dllm_norm_add_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     ("elementwise", "dllm_cast_rows"): [c_void_p, c_void_p, c_longlong, c_void_p],
     ("diff_attention", "dllm_map_prepare"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
@@ -281,13 +281,17 @@ def norm_sum_residual(residual: torch.Tensor, a: torch.Tensor, wa: torch.Tensor,
                                                         _stream()), "norm_sum_residual")
 
 
-def norm_add_residual(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
-    """residual += y / sqrt(mean(y^2) + eps) * weight, row by row, all float32 (a sublayer whose OUTPUT is normed)."""
-    _cuda(residual, y, weight)
+def norm_add_residual(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                      copy: torch.Tensor | None = None) -> None:
+    """residual += y / sqrt(mean(y^2) + eps) * weight, row by row, all float32 (a sublayer whose OUTPUT is normed).
+    With `copy` (bfloat16, the rows' shape) the new rows are also left there rounded: the next product's operand."""
+    _cuda(residual, y, weight, copy)
+    assert copy is None or (copy.dtype == torch.bfloat16 and copy.numel() >= y.numel())
     rows, hidden = y.shape
     assert all(t.dtype == torch.float32 for t in (residual, y, weight))
     assert residual.shape[0] >= rows and residual.shape[1] == hidden and weight.numel() == hidden
-    _check(_fn("elementwise", "dllm_norm_add_residual")(residual.data_ptr(), y.data_ptr(), weight.data_ptr(), rows,
+    _check(_fn("elementwise", "dllm_norm_add_residual")(residual.data_ptr(), y.data_ptr(), weight.data_ptr(),
+                                                        copy.data_ptr() if copy is not None else None, rows,
                                                         hidden, float(eps), _stream()), "norm_add_residual")
 
 
@@ -355,7 +359,7 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | Non
 
 def diff_attention_decode_supported(cache, heads: int, dim: int) -> bool:
     """Whether the kernel that serves a token's whole group of query heads per block takes these sizes (bfloat16, at
-    most 8 query heads per kv head, dim and value_dim multiples of 8, two pages of keys and values in shared memory)."""
+    most 8 query heads per kv head, dim and value_dim multiples of 8, three pages of keys and values in shared memory)."""
     if cache.dtype != torch.bfloat16 or heads % cache.kv_heads or heads // cache.kv_heads > 8:
         return False
     if dim % 8 or cache.value_dim % 8 or cache.value_dim > 256 or cache.page_size != 64:
@@ -366,15 +370,15 @@ def diff_attention_decode_supported(cache, heads: int, dim: int) -> bool:
     while parts < 8 and parts * 2 * cache.value_dim <= 256:
         parts *= 2
     floats = group * 2 * dim + padded * 64 + 4 * padded + 64
-    stages = 2 * 64 * (2 * dim + 8 + cache.value_dim) * 2
+    stages = 3 * 64 * (2 * dim + 8 + cache.value_dim) * 2
     return 4 * floats + max(stages, 4 * parts * padded * cache.value_dim) <= 200 * 1024
 
 
 def diff_attention_decode_splits(tokens: int, kv_heads: int, longest: int) -> int:
     """Into how many stretches a token's keys are cut: enough blocks (tokens x kv heads x stretches) for two a
-    multiprocessor, at most 16 and at most one per page of the longest context."""
+    multiprocessor, at most 16 and at most one per two pages of the longest context."""
     wanted = max(1, (2 * _multiprocessors()) // max(1, tokens * kv_heads))
-    return max(1, min(16, wanted, -(-int(longest) // 64)))
+    return max(1, min(16, wanted, -(-int(longest) // 128)))
 
 
 def diff_attention_decode(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | None, gate_at: int, cache,

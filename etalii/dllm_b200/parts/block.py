@@ -57,15 +57,27 @@ class PreNormMixerBlock:
 
 def stream_input(consumer, x, rt):
     """The stream as `consumer`'s input: a consumer that says so (`accepts_stream`) gets it still in float32 with
-    the rounding pending, anyone else the rounded activations."""
-    operand = StreamOperand(x, rt)
+    the rounding pending, anyone else the rounded activations. Where the kernel that last wrote the stream also left
+    its rounding (`leave_rounded`) and no kernel has run since, that copy is the rounding."""
+    ready = None
+    kept = getattr(rt, "stream_rounded", None)
+    if kept is not None and kept[0] == x.data_ptr() and kept[1] == tuple(x.shape) and kept[2] == ops.launches:
+        ready = kept[3]
+    operand = StreamOperand(x, rt, ready)
     return operand if getattr(consumer, "accepts_stream", False) else operand.tensor()
+
+
+def add_normed_output(norm, x, out, rt) -> None:
+    """x += norm(out); in bfloat16 the same kernel leaves the new rows rounded for whoever reads the stream next."""
+    copy = rt.ws.buffer("stream_operand", tuple(x.shape), rt.dtype) if rt.dtype == torch.bfloat16 else None
+    norm.add_normed(x, out, rt, copy)
+    rt.stream_rounded = (x.data_ptr(), tuple(x.shape), ops.launches, copy) if copy is not None else None
 
 
 class OutputNormBlock:
     """x += mixer_norm(mixer(x)); x += feed_forward_norm(feed_forward(x)). Each sublayer writes its float32 output to
     a work buffer (`epilogue=ops.EPI_STORE_F32`) and the norm adds the normed rows into the stream in one kernel
-    (`add_normed`)."""
+    (`add_normed`), which also leaves the stream's rounding for the next sublayer's products."""
 
     PARTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
@@ -79,9 +91,9 @@ class OutputNormBlock:
         out = rt.ws.buffer("sublayer_out", tuple(x.shape), torch.float32)
         self.mixer.forward(stream_input(self.mixer, x, rt), out, batch, cache, rt, write_cache,
                            epilogue=ops.EPI_STORE_F32)
-        self.mixer_norm.add_normed(x, out, rt)
+        add_normed_output(self.mixer_norm, x, out, rt)
         self.feed_forward.forward(stream_input(self.feed_forward, x, rt), out, batch, rt, epilogue=ops.EPI_STORE_F32)
-        self.feed_forward_norm.add_normed(x, out, rt)
+        add_normed_output(self.feed_forward_norm, x, out, rt)
 
 
 class OutputNormMixerBlock:
@@ -97,7 +109,7 @@ class OutputNormMixerBlock:
         out = rt.ws.buffer("sublayer_out", tuple(x.shape), torch.float32)
         self.mixer.forward(stream_input(self.mixer, x, rt), out, batch, cache, rt, write_cache,
                            epilogue=ops.EPI_STORE_F32)
-        self.mixer_norm.add_normed(x, out, rt)
+        add_normed_output(self.mixer_norm, x, out, rt)
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -30,9 +30,10 @@ class StreamOperand:
     """A sublayer's input that is the residual stream itself: `x` float32, and `tensor()` its rounding to the
     activation type, made once however many products read it."""
 
-    def __init__(self, x: torch.Tensor, rt) -> None:
+    def __init__(self, x: torch.Tensor, rt, ready: torch.Tensor | None = None) -> None:
+        """`ready`: the rounding, where the kernel that last wrote the stream left it."""
         self.x, self.rt, self.shape = x, rt, x.shape
-        self._tensor = None
+        self._tensor = ready
 
     def tensor(self) -> torch.Tensor:
         if self._tensor is None:
@@ -82,9 +83,10 @@ class RMSNorm:
     def lazy(self, x: torch.Tensor, rt) -> NormedInput:
         return NormedInput(self, x, rt)
 
-    def add_normed(self, residual: torch.Tensor, y: torch.Tensor, rt) -> None:
-        """residual += norm(y): for an arrangement that norms a sublayer's output (y float32 [tokens, hidden])."""
-        ops.norm_add_residual(residual, y, self.weight, self.eps)
+    def add_normed(self, residual: torch.Tensor, y: torch.Tensor, rt, copy: torch.Tensor | None = None) -> None:
+        """residual += norm(y): for an arrangement that norms a sublayer's output (y float32 [tokens, hidden]). With
+        `copy` the new rows are also left there in bfloat16."""
+        ops.norm_add_residual(residual, y, self.weight, self.eps, copy)
 
 
 class LayerNorm:
