@@ -16,7 +16,7 @@ from ..config.satavik import SatavikConfig
 from ..parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 
-def mixer_spec(width: int, eps: float, m: dict, prefix: str) -> PartSpec:
+def mixer_spec(width: int, eps: float, m: dict, prefix: str, reader_chunks=None) -> PartSpec:
     shares = m.get("kv_from") is not None
     rot = m.get("rot")
     position = None
@@ -27,7 +27,8 @@ def mixer_spec(width: int, eps: float, m: dict, prefix: str) -> PartSpec:
     params = {"hidden_size": width, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "dim": m["dim"],
               "vdim": m["vdim"], "scale": float(m["scale"]), "diff": float(m["diff"]), "eps": eps,
               "softcap": float(m["softcap"]) if m.get("softcap") is not None else 0.0,
-              "chunk": int(mask["size"]) if mask is not None else None, "position": position, "shares_keys": shares}
+              "chunk": int(mask["size"]) if mask is not None else None, "position": position, "shares_keys": shares,
+              "reader_chunks": reader_chunks}
     p = prefix + "mix."
     names = {"q": p + "q", "q_norm": p + "q.norm", "g": p + "g", "o": p + "o"}
     names.update({name: p + name for name in ("lq1", "lk1", "lq2", "lk2")})
@@ -59,7 +60,11 @@ def build_spec(config: SatavikConfig) -> ModelSpec:
     for index, layer in enumerate(config.layers):
         prefix = f"l{index}."
         norm = lambda name: PartSpec("rmsnorm", {"hidden_size": width, "eps": eps}, {"weight": prefix + name})  # noqa: E731
-        mixer = mixer_spec(width, eps, layer["mixer"], prefix)
+        # a layer's cache entry is read by itself and by the layers that borrow it, each with a mask of its own
+        readers = [other["mixer"] for j, other in enumerate(config.layers)
+                   if j == index or other["mixer"].get("kv_from") == index]
+        sizes = tuple(int(m["mask"]["size"]) if m.get("mask") is not None else None for m in readers)
+        mixer = mixer_spec(width, eps, layer["mixer"], prefix, sizes)
         mlp = layer.get("mlp")
         if mlp is None:
             layers.append(LayerSpec(block="output_norm_mixer", parts={"mixer": mixer, "mixer_norm": norm("norm1")}))

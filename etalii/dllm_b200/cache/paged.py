@@ -32,7 +32,8 @@ class CacheNeed:
     """What one cache entry needs. kind "kv": keys and values of `kv_heads` x `head_dim` per position (values of
     `value_dim` where that is given and differs), all of them (window None), the last `window`, or those of the
     running chunk of `chunk` positions (a mixer whose tokens only look back to the start of their own chunk: positions
-    of chunks that are over are never read again). kind "state": a float32 tensor of `state_shape` per sequence. kind
+    of chunks that are over are never read again; several mixers that read one entry with chunks of their own give a
+    tuple of sizes, and a position is kept while any of them can still see it). kind "state": a float32 tensor of `state_shape` per sequence. kind
     "several": a mixer that keeps more than one thing (keys and values beside a state, two states) lists them in
     `parts`; the model gives every part a cache entry of its own and hands the mixer their views in that order."""
 
@@ -43,7 +44,12 @@ class CacheNeed:
     state_shape: tuple[int, ...] = ()
     parts: tuple["CacheNeed", ...] = ()
     value_dim: int = 0
-    chunk: int | None = None
+    chunk: int | tuple[int, ...] | None = None
+
+    def chunks(self) -> tuple[int, ...]:
+        if not self.chunk:
+            return ()
+        return tuple(self.chunk) if isinstance(self.chunk, (tuple, list)) else (int(self.chunk),)
 
 
 class KvView:
@@ -124,7 +130,7 @@ class PagedCache:
             pages = self.n_pages
             if need.chunk and not need.window:
                 # (as for a window below: every slot's running chunk, and one whole prompt on top)
-                per_sequence = -(-need.chunk // self.page_size) + 1
+                per_sequence = -(-max(need.chunks()) // self.page_size) + 1
                 pages = min(self.n_pages, per_sequence * self.n_slots + -(-self.max_length // self.page_size))
             if need.window:
                 # A windowed group holds at most the window (plus the page being filled) per sequence while it
@@ -175,9 +181,10 @@ class PagedCache:
             first_needed = 0
             if group.need.window:  # positions below (start + 1 - window) are never read again
                 first_needed = max(0, (self.lengths[slot] + 1 - group.need.window)) // self.page_size
-            if group.need.chunk:  # nor are those before the chunk that the first new position lies in
-                first_needed = max(first_needed,
-                                   (self.lengths[slot] // group.need.chunk) * group.need.chunk // self.page_size)
+            if group.need.chunk:  # nor are those before the chunk that the first new position lies in (the
+                # earliest such chunk start, where readers with chunks of different sizes share the entry)
+                start = min((self.lengths[slot] // size) * size for size in group.need.chunks())
+                first_needed = max(first_needed, start // self.page_size)
             if first_needed:
                 for index in range(min(first_needed, len(have))):
                     if have[index] is not None:

@@ -33,7 +33,10 @@ from .spec import ParamSpec
 class DifferentialAttention:
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
                  diff: float, eps: float, softcap: float = 0.0, chunk: int | None = None, window: int | None = None,
-                 position=None, shares_keys: bool = False) -> None:
+                 position=None, shares_keys: bool = False, reader_chunks=None) -> None:
+        """`reader_chunks`: where other mixers read this one's cache entry, the chunk sizes of ALL its readers, this
+        one included (None among them: a reader without chunks); the cache keeps a position while any of them can
+        still see it. Default: this mixer alone."""
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
@@ -42,6 +45,8 @@ class DifferentialAttention:
         self.chunk = int(chunk) if chunk else None
         self.window = int(window) if window else None
         self.shares_keys = bool(shares_keys)
+        readers = (self.chunk,) if reader_chunks is None else tuple(reader_chunks)
+        self.keep_chunks = None if any(not c for c in readers) else tuple(sorted({int(c) for c in readers}))
         self.position = build_part("position", position) if position is not None else None
         self.w_in = self.w_o = self.q_weight = self.k_weight = None
         self.weight = 0.0
@@ -64,7 +69,7 @@ class DifferentialAttention:
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed("kv", kv_heads=self.num_kv_heads, head_dim=2 * self.dim, window=self.window,
-                         value_dim=0 if self.vdim == 2 * self.dim else self.vdim, chunk=self.chunk)
+                         value_dim=0 if self.vdim == 2 * self.dim else self.vdim, chunk=self.keep_chunks)
 
     def bind(self, tensors, rt) -> None:
         # one projection for everything a token needs of h: q, then (a mixer with keys of its own) k and v, then the

@@ -84,6 +84,24 @@ def test_pages_of_finished_chunks_go_back_to_the_pool():
     cache.check()
 
 
+def test_an_entry_with_several_readers_keeps_what_any_of_them_still_sees():
+    """Readers with chunks of 70 and of 100 positions: at position 130 the first still sees from 70 on (page 1), the
+    second from 100; at 140 both chunks begin at or after 100 (page 1 still), at 200 the earliest start is 140 (page 2).
+    And the design's layers hand their masks to the layer whose cache they read."""
+    need = CacheNeed("kv", kv_heads=1, head_dim=8, chunk=(70, 100))
+    cache = PagedCache([need], max_tokens=64 * 12, max_length=64 * 8, max_slots=2)
+    slot = cache.acquire(1)[0]
+    for length, held in ((130, 3), (1, 2), (9, 2), (60, 3), (10, 2)):  # lengths 130, 131, 140, 200, 210
+        cache.reserve(slot, length)
+        cache.advance(slot, length)
+        assert cache.pages_held() == held, (cache.length(slot), cache.pages_held())
+    cache.check()
+    config = config_from_dict(C.CASES["borrowed"]())
+    spec = architecture("Satavik").build_spec(config)
+    assert spec.layers[0].parts["mixer"].params["reader_chunks"] == (48, 33)
+    assert spec.layers[1].parts["mixer"].params["reader_chunks"] == (70, 1000)
+
+
 @pytest.mark.parametrize("case", sorted(C.CASES))
 def test_plain_model_does_not_depend_on_the_cut(case):
     config_dict = C.CASES[case]()

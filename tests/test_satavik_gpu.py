@@ -457,6 +457,21 @@ def test_unequal_batches_early_finishers_and_slots_used_again(name, dtype_name):
 
 
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_pages_behind_a_chunk_stay_while_a_borrowing_layer_still_reads_them(dtype_name):
+    """A layer with chunks of 70 positions lends its keys to a layer with chunks of 1000. A request passes position
+    140; what the lender no longer needs, the borrower still reads, so those pages must not go to the second request,
+    which starts right then and takes whatever pages are free (the most recently freed first). The first layer's
+    entry (chunks of 48 and 33) does give pages back, and they are used again."""
+    case = _case("borrowed")
+    engine = C.make_engine(case.config, case.tensors, dtype_name, max_tokens=64 * 10, max_slots=2)
+    prompts = C.tokens_for(case.config, [150, 60], seed=14)
+    schedule = [[(0, 145)], [(1, 60)]] + [[(0, 1)]] * 5
+    _compare(case, _run(engine, prompts, schedule), prompts, dtype_name)
+    engine.cache.check()
+    assert engine.cache.pages_held() == 0
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
 def test_long_decoding_through_the_decode_graph(dtype_name):
     """A hundred and fifty single-token steps of three sequences as the generation loop runs them (one captured graph
     replayed): they pass several chunk borders, and pages of finished chunks go back to the pool on the way. Then
