@@ -8,7 +8,8 @@
 //               Gate and up rows interleave in the stacked weight [experts, 2 ff, width].
 //   moe_down:   per token: sum over its choices of weight * W_down[expert] act, stored (or added) in float32.
 //
-// A warp owns an output value: its lanes split the reduction in 16-byte pieces, sums in float32. These kernels read an
+// A warp owns a few output values: its lanes split the reduction in 16-byte pieces (the rows' loads asked for together),
+// sums in float32. These kernels read an
 // expert's weights once per token that chose it, which is what a step of few tokens needs.
 #include "common.cuh"
 
@@ -25,20 +26,6 @@ __device__ __forceinline__ float piece(const float* a, const float* b) {
   float4 x = *(const float4*)a, y = *(const float4*)b;
   return fmaf(x.w, y.w, fmaf(x.z, y.z, fmaf(x.y, y.y, x.x * y.x)));
 }
-__device__ __forceinline__ float piece(const __nv_bfloat16* a, const __nv_bfloat16* b) {
-  uint4 ra = *(const uint4*)a, rb = *(const uint4*)b;
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
-  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
-    s = fmaf(x.x, y.x, s);
-    s = fmaf(x.y, y.y, s);
-  }
-  return s;
-}
-
 // This lane's share of a . b over n values (the warp's shares add up to the dot product).
 template <typename T>
 __device__ __forceinline__ float lane_dot(const T* a, const T* b, int n, int lane) {
@@ -49,6 +36,35 @@ __device__ __forceinline__ float lane_dot(const T* a, const T* b, int n, int lan
     for (int d = lane; d < n; d += 32) s = fmaf(to_float(a[d]), to_float(b[d]), s);
   }
   return s;
+}
+
+// This lane's shares of R dot products at once: rows w, w + stride, ... against the same b. The R rows' pieces are
+// asked for together (and b's piece once), so a warp keeps R loads in flight where one row after another keeps one.
+template <int R, typename T>
+__device__ __forceinline__ void lane_dots(const T* w, size_t stride, const T* b, int n, int lane, float* out) {
+#pragma unroll
+  for (int r = 0; r < R; ++r) out[r] = 0.f;
+  bool pieces = n % Vec<T>::N == 0 && (((uintptr_t)w | (uintptr_t)b | (uintptr_t)(stride * sizeof(T))) & 15) == 0;
+  if (pieces) {
+    constexpr int N = Vec<T>::N;
+    for (int d = lane * N; d < n; d += 32 * N) {
+      struct alignas(16) Piece { T v[N]; };
+      Piece held[R], mine;
+#pragma unroll
+      for (int r = 0; r < R; ++r) held[r] = *reinterpret_cast<const Piece*>(w + r * stride + d);
+      mine = *reinterpret_cast<const Piece*>(b + d);
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[r] = fmaf(to_float(held[r].v[i]), to_float(mine.v[i]), out[r]);
+    }
+  } else {
+    for (int d = lane; d < n; d += 32) {
+      float x = to_float(b[d]);
+#pragma unroll
+      for (int r = 0; r < R; ++r) out[r] = fmaf(to_float(w[r * stride + d]), x, out[r]);
+    }
+  }
 }
 
 // The router's weights are float32 whatever the activations are.
@@ -109,25 +125,35 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(
     for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = kept[k] / total;
 }
 
+constexpr int UP_PER_WARP = 2;    // gated values a warp of moe_up owns (four rows of W)
+constexpr int DOWN_PER_WARP = 4;  // output values a warp of moe_down owns
+
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32) moe_up_kernel(
     T* __restrict__ act, const T* __restrict__ h, int width, const T* __restrict__ w_gate_up, int ff, int top,
     const int* __restrict__ chosen, float limit, float alpha, float shift) {
   pdl_launch_dependents();
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int f = blockIdx.y * WARPS + warp;
+  int f = (blockIdx.y * WARPS + warp) * UP_PER_WARP;
   if (f >= ff) return;
   pdl_wait();
   int a = blockIdx.x;
   int e = chosen[a];
   const T* row = h + (size_t)(a / top) * width;
-  const T* wg = w_gate_up + ((size_t)e * 2 * ff + 2 * f) * width;
-  float g = warp_sum(lane_dot(wg, row, width, lane));
-  float u = warp_sum(lane_dot(wg + width, row, width, lane));
-  if (lane == 0) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-    act[(size_t)a * ff + f] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+  const T* wg = w_gate_up + ((size_t)e * 2 * ff + 2 * f) * width;  // rows: gate f, up f, gate f + 1, up f + 1
+  float sums[2 * UP_PER_WARP];
+  if (f + UP_PER_WARP <= ff) {
+    lane_dots<2 * UP_PER_WARP>(wg, (size_t)width, row, width, lane, sums);
+  } else {  // (an odd ff: the last value alone)
+    lane_dots<2>(wg, (size_t)width, row, width, lane, sums);
+    sums[2] = sums[3] = 0.f;
+  }
+#pragma unroll
+  for (int r = 0; r < 2 * UP_PER_WARP; ++r) sums[r] = warp_sum(sums[r]);
+  if (lane < UP_PER_WARP && f + lane < ff) {
+    float g = fminf(lane == 0 ? sums[0] : sums[2], limit);
+    float u = fminf(fmaxf(lane == 0 ? sums[1] : sums[3], -limit), limit);
+    act[(size_t)a * ff + f + lane] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
   }
 }
 
@@ -137,20 +163,39 @@ __global__ void __launch_bounds__(WARPS * 32) moe_down_kernel(
     const int* __restrict__ chosen, const float* __restrict__ weights, int accumulate) {
   pdl_launch_dependents();
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int n = blockIdx.y * WARPS + warp;
+  int n = (blockIdx.y * WARPS + warp) * DOWN_PER_WARP;
   if (n >= width) return;
   pdl_wait();
   int t = blockIdx.x;
-  float sum = 0.f;
+  int count = min(DOWN_PER_WARP, width - n);
+  float total[DOWN_PER_WARP];
+#pragma unroll
+  for (int r = 0; r < DOWN_PER_WARP; ++r) total[r] = 0.f;
   for (int k = 0; k < top; ++k) {
     int a = t * top + k;
     int e = chosen[a];
-    float s = warp_sum(lane_dot(w_down + ((size_t)e * width + n) * ff, act + (size_t)a * ff, ff, lane));
-    sum = fmaf(weights[a], s, sum);
+    const T* w = w_down + ((size_t)e * width + n) * ff;
+    float sums[DOWN_PER_WARP];
+    if (count == DOWN_PER_WARP) {
+      lane_dots<DOWN_PER_WARP>(w, (size_t)ff, act + (size_t)a * ff, ff, lane, sums);
+    } else {
+#pragma unroll
+      for (int r = 0; r < DOWN_PER_WARP; ++r) {
+        sums[r] = 0.f;
+        if (r < count) lane_dots<1>(w + (size_t)r * ff, (size_t)ff, act + (size_t)a * ff, ff, lane, &sums[r]);
+      }
+    }
+    float weight = weights[a];
+#pragma unroll
+    for (int r = 0; r < DOWN_PER_WARP; ++r) total[r] = fmaf(weight, warp_sum(sums[r]), total[r]);
   }
-  if (lane == 0) {
-    size_t at = (size_t)t * width + n;
-    out[at] = accumulate ? out[at] + sum : sum;
+  if (lane < count) {
+    float mine = total[0];
+#pragma unroll
+    for (int r = 1; r < DOWN_PER_WARP; ++r)
+      if (lane == r) mine = total[r];
+    size_t at = (size_t)t * width + n + lane;
+    out[at] = accumulate ? out[at] + mine : mine;
   }
 }
 }  // namespace
@@ -175,7 +220,7 @@ DLLM_EXPORT int dllm_moe_up(void* act, const void* h, int width, const void* w_g
                             const int* chosen, float limit, float alpha, float shift, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return DLLM_OK;
   if (width <= 0 || ff <= 0 || top <= 0 || ff > 65535 * WARPS) return DLLM_UNSUPPORTED_SIZE;
-  dim3 grid(tokens * top, (ff + WARPS - 1) / WARPS), block(WARPS * 32);
+  dim3 grid(tokens * top, (ff + WARPS * UP_PER_WARP - 1) / (WARPS * UP_PER_WARP)), block(WARPS * 32);
   if (dtype == DLLM_F32)
     return dllm_launch_pdl(moe_up_kernel<float>, grid, block, 0, stream, (float*)act, (const float*)h, width,
                            (const float*)w_gate_up, ff, top, chosen, limit, alpha, shift);
@@ -191,7 +236,7 @@ DLLM_EXPORT int dllm_moe_down(float* out, const void* act, int ff, const void* w
                               cudaStream_t stream) {
   if (tokens <= 0) return DLLM_OK;
   if (width <= 0 || ff <= 0 || top <= 0 || width > 65535 * WARPS) return DLLM_UNSUPPORTED_SIZE;
-  dim3 grid(tokens, (width + WARPS - 1) / WARPS), block(WARPS * 32);
+  dim3 grid(tokens, (width + WARPS * DOWN_PER_WARP - 1) / (WARPS * DOWN_PER_WARP)), block(WARPS * 32);
   if (dtype == DLLM_F32)
     return dllm_launch_pdl(moe_down_kernel<float>, grid, block, 0, stream, out, (const float*)act, ff,
                            (const float*)w_down, width, top, chosen, weights, accumulate);

@@ -8,13 +8,13 @@
 //
 // A block owns a tile of 128 places of ONE expert x 128 output features; it finds its expert and rows from the offsets
 // (tiles past the last expert's rows return at once: the grid is sized for the worst case). Operands go through three
-// cp.async stages of 32 reduction values; eight warps of 64 x 32 outputs each. A pair's result does not depend on its
+// cp.async stages of 64 reduction values; eight warps of 64 x 32 outputs each. A pair's result does not depend on its
 // place or on its tile mates, so the arbitrary order inside an expert's list changes no bit.
 #include "common.cuh"
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 256, LDS = BK + 8;
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, THREADS = 256, LDS = BK + 8;
 constexpr int MAX_EXPERTS = 256;
 constexpr int EPI_GLU = 0, EPI_SCATTER = 1;
 
