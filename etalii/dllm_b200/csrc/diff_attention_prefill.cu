@@ -41,6 +41,12 @@ __device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 1 / x with the hardware approximation (about one unit in the last place; 1 / inf = 0).
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -134,7 +140,11 @@ __global__ void __launch_bounds__(THREADS) diff_prefill_kernel(bf16* __restrict_
   int row_pos[2] = {pos0 + warp * 16 + gq, pos0 + warp * 16 + gq + 8};
   int row_first[2] = {first_visible(row_pos[0], a.chunk, a.window), first_visible(row_pos[1], a.chunk, a.window)};
   int warp_last_first = first_visible(pos0 + warp * 16 + 15, a.chunk, a.window);  // the warp's latest first key
-  float cap_in = a.softcap > 0.f ? 2.0f * LOG2E / a.softcap : 0.f;
+  // Scores are kept in units of log2 e (the softmax then needs no multiplication before its exponential). With a cap:
+  // cap tanh(x / cap) = cap - 2 cap / (e^(2 x / cap) + 1), so score' = cap_at - cap_twice / (2^(s * in_scale) + 1).
+  bool capped = a.softcap > 0.f;
+  float in_scale = capped ? a.scale * 2.0f * LOG2E / a.softcap : a.scale * LOG2E;
+  float cap_at = a.softcap * LOG2E, cap_twice = -2.0f * a.softcap * LOG2E;
 
   for (int kt = kt_begin; kt <= kt_end; ++kt) {
     int stage = (kt - kt_begin) & 1;
@@ -159,14 +169,13 @@ __global__ void __launch_bounds__(THREADS) diff_prefill_kernel(bf16* __restrict_
         mma_bf16(s[2 * jp + 1], q_frag[ks], bfr[2], bfr[3]);
       }
     }
-    // scale, cap, masks
+    // scale, cap (in units of log2 e), masks
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        float v = s[j][r] * a.scale;
-        if (a.softcap > 0.f)  // cap * tanh(v / cap) = cap * (1 - 2 / (e^(2 v / cap) + 1))
-          v = a.softcap * (1.0f - __fdividef(2.0f, fast_exp2(v * cap_in) + 1.0f));
+        float v = s[j][r] * in_scale;
+        if (capped) v = fmaf(cap_twice, fast_rcp(fast_exp2(v) + 1.0f), cap_at);
         s[j][r] = v;
       }
     int key0 = kt * BN;
@@ -192,16 +201,16 @@ __global__ void __launch_bounds__(THREADS) diff_prefill_kernel(bf16* __restrict_
       tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
       float m_new = fmaxf(m_run[i], tile_max[i]);
       float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that sees nothing in this tile (and nothing before)
-      corr[i] = fast_exp2((m_run[i] - m_use) * LOG2E);
+      corr[i] = fast_exp2(m_run[i] - m_use);
       m_run[i] = m_new;
-      tile_max[i] = m_use * LOG2E;
+      tile_max[i] = m_use;
     }
     float row_sum[2] = {0.f, 0.f};
     unsigned p_frag[BN / 16][4];
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j) {
-      float p0 = fast_exp2(fmaf(s[j][0], LOG2E, -tile_max[0])), p1 = fast_exp2(fmaf(s[j][1], LOG2E, -tile_max[0]));
-      float p2 = fast_exp2(fmaf(s[j][2], LOG2E, -tile_max[1])), p3 = fast_exp2(fmaf(s[j][3], LOG2E, -tile_max[1]));
+      float p0 = fast_exp2(s[j][0] - tile_max[0]), p1 = fast_exp2(s[j][1] - tile_max[0]);
+      float p2 = fast_exp2(s[j][2] - tile_max[1]), p3 = fast_exp2(s[j][3] - tile_max[1]);
       row_sum[0] += p0 + p1;
       row_sum[1] += p2 + p3;
       p_frag[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
