@@ -1,12 +1,16 @@
 // Differential attention of steps of single tokens (bfloat16 cache). A block serves one token and one kv head, that is
 // ALL query heads of the group and both of their score maps (an "item" is a (head, map) pair), over one stretch of the
 // keys the token sees; `splits` blocks share a token's keys, and the block that finishes last combines their partial
-// results in stretch order (a ticket counter: nobody waits). Keys and values come page by page (64 positions) into three
-// shared-memory stages by cp.async (two pages on their way while one is worked on), so a page's latency is paid once:
+// results in stretch order (a ticket counter: nobody waits). Keys and values come page by page (64 positions) into two
+// shared-memory stages by cp.async (the next page on its way while one is worked on; two blocks share a
+// multiprocessor), so a page's latency is paid once:
 //
-//   scores:   a thread per (head, key): both maps' q . k from shared memory, scale, cap * tanh(score / cap), masks
+//   scores:   on the tensor cores (mma.sync m16n8k16) where dim and vdim are multiples of 16: the group's heads are the
+//             rows of a tile, a warp per map and sixteen keys; else a thread per (head, key) from shared memory; then
+//             scale, cap * tanh(score / cap), masks, in float32
 //   softmax:  a warp per item: the page's maximum, the running maximum and sum, the weights in place of the scores
-//   values:   a thread per value place (and part of the page): every item's weighted sum gets the page's share
+//   values:   on the tensor cores too (the items are the rows, a warp per 16 value places, the weights rounded to
+//             bfloat16 as that product's operand only); else a thread per value place and part of the page
 //
 // and at the end a1 - weight * a2 per head, over its root mean square, times the scale and the head's gate. All of
 // it float32 except the cache. A token's result does not depend on its batch mates; the stretches are cut by page
@@ -16,7 +20,7 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int THREADS = 256, WARPS = 8, PAGE = 64, MAX_ITEMS = 16, STAGES = 3;
+constexpr int THREADS = 256, WARPS = 8, PAGE = 64, MAX_ITEMS = 16, STAGES = 2;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -24,6 +28,25 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned* r, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned* r, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int LDP = PAGE + 8;  // a row of weights as a tensor-core operand
 
 struct DecodeArgs {
   const float* q;      // [tokens, heads, 2, dim] float32, normed and rotated
@@ -62,7 +85,13 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
   float* red_s = state_s + 4 * ITEMS;                               // [WARPS][MAX_ITEMS / 2] sums of squares (the state
                                                                     // takes four rows: what follows starts on 16 bytes)
   bf16* k_s = reinterpret_cast<bf16*>(red_s + WARPS * (MAX_ITEMS / 2));  // [STAGES][PAGE][ldk]
-  bf16* v_s = k_s + STAGES * PAGE * ldk;                            // [STAGES][PAGE][vdim]
+  int ldv = vdim + 8, ldq = dim + 8;
+  bf16* v_s = k_s + STAGES * PAGE * ldk;                            // [STAGES][PAGE][ldv]
+  bf16* q_b = v_s + STAGES * PAGE * ldv;                            // [2 maps][16 rows][ldq]: the queries as an operand
+  bf16* p_b = q_b + 2 * 16 * ldq;                                   // [16 rows][LDP]: a page's weights as an operand
+  // With sizes that tile (16 values a step), scores and weighted sums run on the tensor cores: the group's heads are
+  // the rows of the score tiles (one product per map), the items the rows of the value tiles.
+  bool tensor = dim % 16 == 0 && vdim % 16 == 0;
   pdl_launch_dependents();
   pdl_wait();
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -83,20 +112,36 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
     state_s[ITEMS + tid] = 0.f;
     state_s[2 * ITEMS + tid] = 1.f;
   }
+  if (tensor) {
+    for (int row = warp; row < 2 * 16; row += WARPS) {  // a warp per (map, head) row
+      int m = row >> 4, r = row & 15;
+      for (int c = lane; c < ldq; c += 32)
+        q_b[row * ldq + c] = __float2bfloat16_rn(r < group && c < dim ? qrow[(size_t)r * 2 * dim + m * dim + c] : 0.f);
+    }
+    for (int i = tid; i < 16 * LDP; i += THREADS) p_b[i] = __float2bfloat16_rn(0.f);
+  }
   const bf16* base = (const bf16*)cache.base;
   int k_pieces = key_dim >> 3, v_pieces = vdim >> 3;
+  // A page's rows are copied by warps: a row takes `k_lanes` (`v_lanes`) lanes, a power of two, so a lane finds its
+  // row and piece by shifts (divisions by the piece counts cost more than the copies they would steer).
+  int k_lanes = 1, v_lanes = 1;
+  while (k_lanes < k_pieces && k_lanes < 32) k_lanes <<= 1;
+  while (v_lanes < v_pieces && v_lanes < 32) v_lanes <<= 1;
+  int k_row = tid / k_lanes, k_piece = tid % k_lanes, k_rows = THREADS / k_lanes;  // (powers of two: shifts)
+  int v_row = tid / v_lanes, v_piece = tid % v_lanes, v_rows = THREADS / v_lanes;
   auto load_page = [&](int stage, int p) {
     int page = pages[p];
     const bf16* ksrc = base + key_at(cache, page, g, 0);
     const bf16* vsrc = base + value_at(cache, page, g, 0);
-    for (int i = tid; i < PAGE * k_pieces; i += THREADS) {
-      int r = i / k_pieces, c = (i % k_pieces) * 8;
-      cp_async_16(k_s + (stage * PAGE + r) * ldk + c, ksrc + (size_t)r * key_dim + c);
-    }
-    for (int i = tid; i < PAGE * v_pieces; i += THREADS) cp_async_16(v_s + (size_t)stage * PAGE * vdim + i * 8, vsrc + i * 8);
+    for (int r = k_row; r < PAGE; r += k_rows)
+      for (int c = k_piece; c < k_pieces; c += k_lanes)
+        cp_async_16(k_s + (stage * PAGE + r) * ldk + c * 8, ksrc + (size_t)r * key_dim + c * 8);
+    for (int r = v_row; r < PAGE; r += v_rows)
+      for (int c = v_piece; c < v_pieces; c += v_lanes)
+        cp_async_16(v_s + (stage * PAGE + r) * ldv + c * 8, vsrc + (size_t)r * vdim + c * 8);
   };
 #pragma unroll
-  for (int ahead = 0; ahead < STAGES - 1; ++ahead) {  // two pages on their way before the first is used
+  for (int ahead = 0; ahead < STAGES - 1; ++ahead) {  // pages on their way before the first is used
     if (p_begin + ahead < p_end) load_page(ahead, p_begin + ahead);
     cp_async_commit();
   }
@@ -110,6 +155,14 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
   float acc[ITEMS];
 #pragma unroll
   for (int it = 0; it < ITEMS; ++it) acc[it] = 0.f;
+  float tile_acc[2][2][4];  // tensor path: two groups of 16 value places a warp, rows gq and gq + 8
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) tile_acc[i][j][r] = 0.f;
+  int gq = lane >> 2, tq = lane & 3, mat = lane >> 3;
   __syncthreads();
 
   for (int p = p_begin; p < p_end; ++p) {
@@ -119,6 +172,30 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
     if (p + STAGES - 1 < p_end) load_page((stage + STAGES - 1) % STAGES, p + STAGES - 1);
     cp_async_commit();
     // scores
+    if (tensor) {
+      int m = warp >> 2, quarter = warp & 3;  // a warp: one map, sixteen keys
+      float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      for (int ks = 0; ks < dim / 16; ++ks) {
+        unsigned af[4], bfr[4];
+        ldmatrix_x4(af, q_b + (m * 16 + (lane & 15)) * ldq + ks * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(bfr, k_s + (stage * PAGE + quarter * 16 + (mat >> 1) * 8 + (lane & 7)) * ldk + m * dim + ks * 16 +
+                             (mat & 1) * 8);
+        mma_bf16(c[0], af, bfr[0], bfr[1]);
+        mma_bf16(c[1], af, bfr[2], bfr[3]);
+      }
+      if (gq < group) {
+#pragma unroll
+        for (int nj = 0; nj < 2; ++nj)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            int key = quarter * 16 + nj * 8 + tq * 2 + e;
+            int key_pos = p * PAGE + key;
+            float v = c[nj][e] * a.scale;
+            if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+            s_s[(gq * 2 + m) * PAGE + key] = key_pos >= first && key_pos < end ? v : -INFINITY;
+          }
+      }
+    } else
     for (int idx = tid; idx < group * PAGE; idx += THREADS) {
       int head = idx / PAGE, key = idx % PAGE;
       int key_pos = p * PAGE + key;
@@ -149,6 +226,10 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
       float sum = warp_sum(p0 + p1);
       s_s[it * PAGE + lane] = p0;
       s_s[it * PAGE + 32 + lane] = p1;
+      if (tensor) {
+        p_b[it * LDP + lane] = __float2bfloat16_rn(p0);
+        p_b[it * LDP + 32 + lane] = __float2bfloat16_rn(p1);
+      }
       if (lane == 0) {
         state_s[it] = m_new;
         state_s[ITEMS + it] = state_s[ITEMS + it] * corr + sum;
@@ -157,13 +238,35 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
     }
     __syncthreads();
     // values
-    if (has_values) {
+    if (tensor) {
+      float corr_lo = gq < items ? state_s[2 * ITEMS + gq] : 1.f, corr_hi = gq + 8 < items ? state_s[2 * ITEMS + gq + 8] : 1.f;
+      unsigned af[PAGE / 16][4];
+#pragma unroll
+      for (int kk = 0; kk < PAGE / 16; ++kk) ldmatrix_x4(af[kk], p_b + (lane & 15) * LDP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int gi = 0; gi < 2; ++gi) {
+        int columns = (warp + gi * WARPS) * 16;  // this warp's gi-th group of 16 value places
+        if (columns >= vdim) break;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          tile_acc[gi][j][0] *= corr_lo; tile_acc[gi][j][1] *= corr_lo;
+          tile_acc[gi][j][2] *= corr_hi; tile_acc[gi][j][3] *= corr_hi;
+        }
+#pragma unroll
+        for (int kk = 0; kk < PAGE / 16; ++kk) {
+          unsigned bfr[4];
+          ldmatrix_x4_trans(bfr, v_s + (stage * PAGE + kk * 16 + (mat & 1) * 8 + (lane & 7)) * ldv + columns + (mat >> 1) * 8);
+          mma_bf16(tile_acc[gi][0], af[kk], bfr[0], bfr[1]);
+          mma_bf16(tile_acc[gi][1], af[kk], bfr[2], bfr[3]);
+        }
+      }
+    } else if (has_values) {
 #pragma unroll
       for (int it = 0; it < ITEMS; ++it) acc[it] *= state_s[2 * ITEMS + it];
-      const bf16* vb = v_s + (size_t)stage * PAGE * vdim + d;
+      const bf16* vb = v_s + (size_t)stage * PAGE * ldv + d;
       for (int j = part * j_per; j < (part + 1) * j_per; j += 4) {
-        float v0 = __bfloat162float(vb[(size_t)j * vdim]), v1 = __bfloat162float(vb[(size_t)(j + 1) * vdim]);
-        float v2 = __bfloat162float(vb[(size_t)(j + 2) * vdim]), v3 = __bfloat162float(vb[(size_t)(j + 3) * vdim]);
+        float v0 = __bfloat162float(vb[(size_t)j * ldv]), v1 = __bfloat162float(vb[(size_t)(j + 1) * ldv]);
+        float v2 = __bfloat162float(vb[(size_t)(j + 2) * ldv]), v3 = __bfloat162float(vb[(size_t)(j + 3) * ldv]);
 #pragma unroll
         for (int it = 0; it < ITEMS; ++it) {
           if (it < items) {
@@ -178,7 +281,28 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
   cp_async_wait<0>();
   // the parts' sums meet in the threads of part 0 (through the key/value space, free now)
   float* meet = reinterpret_cast<float*>(k_s);  // [parts][ITEMS][vdim]
-  if (parts > 1) {
+  if (tensor) {
+    // the tiles' rows (items) and columns (value places) go to the threads that own a value place each
+    __syncthreads();
+#pragma unroll
+    for (int gi = 0; gi < 2; ++gi) {
+      int columns = (warp + gi * WARPS) * 16;
+      if (columns >= vdim) break;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          int row = gq + (r >> 1) * 8, col = columns + j * 8 + tq * 2 + (r & 1);
+          if (row < items) meet[(size_t)row * vdim + col] = tile_acc[gi][j][r];
+        }
+    }
+    __syncthreads();
+    if (tid < vdim)
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it)
+        if (it < items) acc[it] = meet[(size_t)it * vdim + d];
+    __syncthreads();  // (the space serves again below)
+  } else if (parts > 1) {
     __syncthreads();
     if (has_values && part > 0)
 #pragma unroll
@@ -278,11 +402,12 @@ __global__ void __launch_bounds__(THREADS) diff_decode_kernel(bf16* __restrict__
 
 size_t shared_bytes(int group, int dim, int vdim, int items_padded) {
   size_t floats = (size_t)group * 2 * dim + (size_t)items_padded * PAGE + 4 * items_padded + WARPS * (MAX_ITEMS / 2);
-  size_t stages = STAGES * (size_t)PAGE * (2 * dim + 8 + vdim) * sizeof(bf16);
+  size_t stages = STAGES * (size_t)PAGE * (2 * dim + 8 + vdim + 8) * sizeof(bf16);
+  size_t operands = ((size_t)2 * 16 * (dim + 8) + 16 * LDP) * sizeof(bf16);
   int parts = 1;
   while (parts < 8 && parts * 2 * vdim <= THREADS) parts *= 2;
   size_t meet = (size_t)parts * items_padded * vdim * sizeof(float);  // (shares the stages' space)
-  return floats * sizeof(float) + (stages > meet ? stages : meet);
+  return floats * sizeof(float) + (stages > meet ? stages : meet) + operands;
 }
 
 template <int ITEMS>

@@ -357,21 +357,19 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, gates: torch.Tensor | Non
         lambda: f"dim={dim}, value_dim={cache.value_dim} (at most 256)")
 
 
+_decode_fits: dict[tuple, bool] = {}
+
+
 def diff_attention_decode_supported(cache, heads: int, dim: int) -> bool:
     """Whether the kernel that serves a token's whole group of query heads per block takes these sizes (bfloat16, at
-    most 8 query heads per kv head, dim and value_dim multiples of 8, three pages of keys and values in shared memory)."""
-    if cache.dtype != torch.bfloat16 or heads % cache.kv_heads or heads // cache.kv_heads > 8:
+    most 8 query heads per kv head, dim and value_dim multiples of 8, the stages of keys and values in shared memory:
+    the library itself says)."""
+    if cache.dtype != torch.bfloat16 or heads % cache.kv_heads:
         return False
-    if dim % 8 or cache.value_dim % 8 or cache.value_dim > 256 or cache.page_size != 64:
-        return False
-    group = heads // cache.kv_heads
-    padded = next(n for n in (2, 4, 8, 16) if 2 * group <= n)
-    parts = 1
-    while parts < 8 and parts * 2 * cache.value_dim <= 256:
-        parts *= 2
-    floats = group * 2 * dim + padded * 64 + 4 * padded + 64
-    stages = 3 * 64 * (2 * dim + 8 + cache.value_dim) * 2
-    return 4 * floats + max(stages, 4 * parts * padded * cache.value_dim) <= 200 * 1024
+    key = (heads, cache.kv_heads, dim, cache.value_dim, cache.page_size)
+    if key not in _decode_fits:
+        _decode_fits[key] = _fn("diff_attention_decode", "dllm_diff_attention_decode_fits")(*key) == 0
+    return _decode_fits[key]
 
 
 def diff_attention_decode_splits(tokens: int, kv_heads: int, longest: int) -> int:

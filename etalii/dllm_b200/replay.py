@@ -18,16 +18,21 @@ import sys
 from typing import IO, Iterable
 
 
+SPARE_PAGES = 16
+"""Pages of 64 tokens beyond `--max-tokens`: room for the unused ends of the live requests' last pages."""
+
+
 def run(model: str, dtype: str, out: str, max_tokens: int, device: str = "cuda:0",
         lines: Iterable[str] | None = None, report: IO[str] | None = None) -> int:
     """Replays the steps read from `lines` (default: standard input). `max_tokens`: the most tokens live requests
-    hold at any time, each request's count rounded up to a multiple of 64; it sizes the cache exactly."""
+    hold at any time; it sizes the cache: that many tokens in pages of 64, and `SPARE_PAGES` more, since every live
+    request's last page is only partly full and a count without that padding would leave the cache short."""
     from .engine.engine import Engine
 
     lines = sys.stdin if lines is None else lines
     report = sys.stdout if report is None else report
     os.makedirs(out, exist_ok=True)
-    pages = -(-int(max_tokens) // 64)
+    pages = -(-int(max_tokens) // 64) + SPARE_PAGES
     engine = Engine.from_folder(model, dtype=dtype, device=device, max_tokens=pages * 64, max_length=pages * 64,
                                 max_slots=pages)
     slots: dict[str, int] = {}
