@@ -1,5 +1,5 @@
 """Small Satavik configurations and random weights for the tests: sizes that are no powers of two, one and several
-key/value heads, values wider and narrower than the two maps' keys, part and no rotation, chunks that are no multiple
+key/value heads, values wider and narrower than the two maps' keys and as wide, part and no rotation, chunks that are no multiple
 of a page, layers that borrow another layer's keys, a layer without a feed-forward, one expert of three and three of
 five, with and without a shared expert."""
 from __future__ import annotations
@@ -41,6 +41,13 @@ CASES = {
                   mlp=moe(ff=16, experts=3, top=1, shared_ff=0)),
         attention(kv_from=0, chunk=33, scale=0.21, softcap=50.0, diff=0.1, mlp=None),
         attention(heads=4, kv_heads=1, dim=24, vdim=48, rot_dims=24, base=77.0, chunk=1000, kv_from=1, diff=0.4)]),
+    # sizes that tile for the tensor cores (maps of 32, values of 64), four query heads per kv head, two kv heads; the
+    # second layer borrows with a smaller chunk
+    "tiled": lambda: config([
+        attention(heads=8, kv_heads=2, dim=32, vdim=64, rot_dims=16, chunk=96, scale=0.18, softcap=15.0,
+                  mlp=moe(ff=32, experts=4, top=2, shared_ff=16)),
+        attention(heads=8, kv_heads=2, dim=32, vdim=64, rot_dims=16, chunk=40, scale=0.18, softcap=15.0, kv_from=0,
+                  mlp=moe(ff=32, experts=4, top=2, shared_ff=16))], width=128, vocab=211),
     # a map size that is no multiple of 8 (no 16-byte pieces), narrow values, no rotation at all, one head, a chunk of
     # five positions, two experts of two
     "narrow": lambda: config([
